@@ -1,0 +1,90 @@
+"""ctypes loader for the sm_100a kernel library.
+
+The library is built by :mod:`nano_megatron_b200.build` and lives next to the
+package as ``libnmb_kernels.so``.  On a machine with a CUDA device a missing
+library is an error (the ops never fall back silently to PyTorch on a GPU);
+without a device the library is simply not needed.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "libnmb_kernels.so"
+_lib: Optional[ctypes.CDLL] = None
+_lock = threading.Lock()
+
+STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "peer flag wait timed out",
+                3: "bad argument", 4: "size beyond the supported maximum"}
+
+
+class NativeKernelError(RuntimeError):
+    """A kernel launcher or a device-side bounded wait reported a failure."""
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the kernel library."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not _LIB_PATH.exists():
+                    raise NativeKernelError(
+                        f"{_LIB_PATH} is missing: run `python -m nano_megatron_b200.build` "
+                        "(the CUDA ops do not fall back to PyTorch on a GPU)"
+                    )
+                _lib = ctypes.CDLL(str(_LIB_PATH))
+    return _lib
+
+
+def ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream_ptr(device: torch.device | None = None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels write on a timed-out wait."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    w = _status_words.get(idx)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status_words[idx] = w
+    return w
+
+
+def check_status(device: torch.device | None = None, *, reset: bool = True) -> None:
+    """Read the status word (host sync) and raise if a kernel reported a failure."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    w = status_word(device)
+    v = int(w.item())
+    if v != 0:
+        if reset:
+            w.zero_()
+        code, where = v & 0xFF, v >> 8
+        raise NativeKernelError(
+            f"device-side failure: {STATUS_NAMES.get(code, code)} (site {where})"
+        )
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc != 0:
+        raise NativeKernelError(f"{what}: launcher returned {rc}")
