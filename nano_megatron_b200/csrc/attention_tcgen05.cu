@@ -1,0 +1,817 @@
+// Causal flash attention forward / backward on tcgen05 tensor cores.
+//
+// Replaces the flash-attn 2.x calls of the reference
+// (nano_megatron/parallel/attention_backend.py:216-223 forward,
+// :497-514 chunked backward) and, because the key/value side is described by
+// up to eight tensor maps ("chunks"), also the context-parallel path
+// (:355-530, :549-635): each chunk may live in another GPU's memory and is
+// fetched tile by tile with plain (non-multicast) TMA loads, so no gathered
+// K/V copy is ever materialised and the online-softmax merge across chunks
+// happens in registers.
+//
+// Layout: all tensors are addressed through 4-D tensor maps
+// {head_dim, seq, heads, batch} with arbitrary strides, so the fused-QKV GEMM
+// output [B*S, 3H] is consumed in place and the context is written in the
+// [B*S, H] layout the output projection reads -- none of the
+// split-heads / merge-heads / repeat_kv copies of the reference
+// (nano_megatron/model/tp_gpt.py:171-187) exist here.
+//
+// Forward CTA = one 128-row query tile of one head; 192 threads:
+//   warps 0-3  online softmax (one query row per thread), O rescale, epilogue
+//   warp 4     TMA producer (K/V double buffered)
+//   warp 5     TMEM owner + tcgen05.mma issuer
+// S = Q K^T lives in TMEM (128 fp32 columns), P is written back to shared
+// memory as a K-major bf16 operand, O accumulates in TMEM.
+//
+// Backward CTA = one 128-row key/value tile of one KV head, looping over the
+// query tiles that can see it; dK/dV accumulate in TMEM, dQ tiles are added
+// to an fp32 buffer with reductions.
+#include "common.cuh"
+
+namespace nmb {
+
+constexpr int kMaxChunks = 8;
+constexpr int kAttnThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnFwdParams {
+  CUtensorMap q_map;
+  CUtensorMap k_map[kMaxChunks];
+  CUtensorMap v_map[kMaxChunks];
+  __nv_bfloat16* o;
+  float* lse;  // [B, Hq, Sq]
+  long long o_stride_b, o_stride_s, o_stride_h;
+  int B, Hq, Hkv, Sq;
+  int chunk_len, n_chunks;
+  int d;       // true head dim (64, 96 or 128)
+  int q_pos0;  // global position of query row 0 (context parallel offset)
+  float scale;
+  int* status;
+};
+
+template <int HD>
+struct AttnFwdSmem {
+  static constexpr int kSlabs = HD / 64;
+  static constexpr int kTile = kSlabs * 16384;   // one 128 x HD bf16 tile
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTile;          // 2 stages
+  static constexpr int kV = kK + 2 * kTile;      // 2 stages
+  static constexpr int kP = kV + 2 * kTile;      // 128 x 128 bf16
+  static constexpr int kBar = kP + 32768;
+  static constexpr int kNumBars = 9;
+  static constexpr int kTotal = kBar + kNumBars * 8 + 16;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, HD == 64 ? 2 : 1)
+attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
+  using L = AttnFwdSmem<HD>;
+  constexpr int NS = L::kSlabs;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* q_full = &bars[0];
+  uint64_t* kv_full = &bars[1];   // [2]
+  uint64_t* kv_empty = &bars[3];  // [2]
+  uint64_t* s_full = &bars[5];
+  uint64_t* s_empty = &bars[6];
+  uint64_t* p_full = &bars[7];
+  uint64_t* o_full = &bars[8];
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(&bars[L::kNumBars]);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_q_tiles = gridDim.x;
+  const int qt = n_q_tiles - 1 - blockIdx.x;  // longest tiles first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qt * 128;
+  const int skv_total = p.chunk_len * p.n_chunks;
+  int q_last = q0 + 127;
+  if (q_last > p.Sq - 1) q_last = p.Sq - 1;
+  int n_kv = (p.q_pos0 + q_last + 128) / 128;  // ceil((last_pos + 1) / 128)
+  const int max_kv = (skv_total + 127) / 128;
+  if (n_kv > max_kv) n_kv = max_kv;
+  constexpr uint32_t kTmemCols = 256;  // S: 128, O: HD <= 128
+  constexpr uint32_t kSCol = 0, kOCol = 128;
+
+  if ((smem_u32(smem) & 1023u) != 0) {  // swizzled operands need 1 KiB alignment
+    if (threadIdx.x == 0) report_status(p.status, kBadArgument, 20);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 128);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      tma_prefetch_desc(&p.q_map);
+      mbar_expect_tx(q_full, L::kTile);
+#pragma unroll
+      for (int c = 0; c < NS; ++c)
+        tma_load_4d(smem + L::kQ + c * 16384, &p.q_map, q_full, c * 64, q0, h, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        if (j >= 2 && !mbar_wait(&kv_empty[st], ((j >> 1) - 1) & 1, abort_flag, p.status, 21)) break;
+        const int chunk = (j * 128) / p.chunk_len;
+        const int row0 = j * 128 - chunk * p.chunk_len;
+        mbar_expect_tx(&kv_full[st], 2 * L::kTile);
+#pragma unroll
+        for (int c = 0; c < NS; ++c) {
+          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &p.k_map[chunk], &kv_full[st], c * 64,
+                      row0, hk, b);
+          tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &p.v_map[chunk], &kv_full[st], c * 64,
+                      row0, hk, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, HD, false, true);
+      const uint32_t sQ = smem_u32(smem + L::kQ);
+      const uint32_t sP = smem_u32(smem + L::kP);
+      auto issue_qk = [&](int j) {
+        const uint32_t sK = smem_u32(smem + L::kK + (j & 1) * L::kTile);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          tc_mma_bf16(tmem_base + kSCol, make_smem_desc(sQ + off, 16, 1024),
+                      make_smem_desc(sK + off, 16, 1024), idesc_qk, k != 0 ? 1u : 0u);
+        }
+        tc_commit(s_full);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 22) &&
+                mbar_wait(&kv_full[0], 0, abort_flag, p.status, 23);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          // S is single buffered: the next QK^T may start once the softmax
+          // warps have read S_j; it then overlaps their P write / O rescale.
+          if (!mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.status, 24) ||
+              !mbar_wait(s_empty, j & 1, abort_flag, p.status, 25)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_qk(j + 1);
+        }
+        if (!mbar_wait(p_full, j & 1, abort_flag, p.status, 26)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sV = smem_u32(smem + L::kV + (j & 1) * L::kTile);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          tc_mma_bf16(tmem_base + kOCol,
+                      make_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                      make_smem_desc(sV + k * 2048, 16384, 1024), idesc_pv, (j | k) != 0 ? 1u : 0u);
+        }
+        tc_commit(o_full);
+        tc_commit(&kv_empty[j & 1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------- softmax + epilogue --
+    const int r = threadIdx.x;  // query row in the tile == TMEM lane
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const int q_row = q0 + r;
+    const int q_pos = p.q_pos0 + q_row;
+    const float sl2 = p.scale * kLog2e;
+    float m_run = -INFINITY;
+    float l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(s_full, j & 1, abort_flag, p.status, 27)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int kv0 = j * 128;
+      int limit = q_pos - kv0;                       // columns <= limit are visible
+      if (skv_total - 1 - kv0 < limit) limit = skv_total - 1 - kv0;
+      // pass 1: running maximum
+      float mx = m_run;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32];
+        tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const float s = (c * 32 + jj <= limit) ? __uint_as_float(sr[jj]) : -INFINITY;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = mx;
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_use) * sl2);
+      // pass 2: probabilities
+      uint32_t pk[64];
+      float rowsum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32];
+        tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) {
+          const float s0 = __uint_as_float(sr[jj]);
+          const float s1 = __uint_as_float(sr[jj + 1]);
+          const float p0 = (c * 32 + jj <= limit) ? exp2f((s0 - m_use) * sl2) : 0.f;
+          const float p1 = (c * 32 + jj + 1 <= limit) ? exp2f((s1 - m_use) * sl2) : 0.f;
+          rowsum += p0 + p1;
+          pk[c * 16 + jj / 2] = pack_bf16x2(p0, p1);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(s_empty);
+      l_run = l_run * alpha + rowsum;
+      m_run = m_new;
+      if (j > 0) {
+        if (!mbar_wait(o_full, (j - 1) & 1, abort_flag, p.status, 28)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld_32x32(t_lane + kOCol + c * 32, orr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) orr[jj] = __float_as_uint(__uint_as_float(orr[jj]) * alpha);
+            tmem_st_32x32(t_lane + kOCol + c * 32, orr);
+          }
+          tmem_st_wait();
+        }
+      }
+      // P -> shared memory, K-major, 128-byte swizzle (two 64-column slabs).
+      uint8_t* sp = smem + L::kP;
+#pragma unroll
+      for (int c16 = 0; c16 < 16; ++c16) {
+        uint4 u = make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
+        *reinterpret_cast<uint4*>(sp + (c16 >> 3) * 16384 + swz128_offset(r, c16 & 7)) = u;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(o_full, (n_kv - 1) & 1, abort_flag, p.status, 29)) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* orow = p.o + b * p.o_stride_b + static_cast<long long>(q_row) * p.o_stride_s +
+                            h * p.o_stride_h;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t orr[32];
+        tmem_ld_32x32(t_lane + kOCol + c * 32, orr);
+        tmem_ld_wait();
+        if (q_row < p.Sq && c * 32 < p.d) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(orr[q * 8 + 0]) * inv, __uint_as_float(orr[q * 8 + 1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(orr[q * 8 + 2]) * inv, __uint_as_float(orr[q * 8 + 3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(orr[q * 8 + 4]) * inv, __uint_as_float(orr[q * 8 + 5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(orr[q * 8 + 6]) * inv, __uint_as_float(orr[q * 8 + 7]) * inv);
+            dst[q] = u;
+          }
+        }
+      }
+      if (q_row < p.Sq)
+        p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + q_row] = m_run * p.scale + logf(l_run);
+    }
+  }
+
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ backward --
+struct AttnBwdParams {
+  CUtensorMap q_map;
+  CUtensorMap do_map;
+  CUtensorMap k_map[kMaxChunks];
+  CUtensorMap v_map[kMaxChunks];
+  __nv_bfloat16* dk[kMaxChunks];  // per chunk: where this rank's dK / dV tiles go
+  __nv_bfloat16* dv[kMaxChunks];
+  long long dkv_stride_b, dkv_stride_s, dkv_stride_h;
+  const float* lse;    // [B, Hq, Sq]
+  const float* delta;  // [B, Hq, Sq]  rowsum(dO * O)
+  float* dq_acc;       // [B, Sq, Hq, d] fp32, zero-initialised
+  int B, Hq, Hkv, Sq;
+  int chunk_len, n_chunks;
+  int d;
+  int q_pos0;
+  float scale;
+  int* status;
+};
+
+template <int HD>
+struct AttnBwdSmem {
+  static constexpr int kSlabs = HD / 64;
+  static constexpr int kTile = kSlabs * 16384;
+  static constexpr int kQStages = HD == 64 ? 2 : 1;
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTile;
+  static constexpr int kQ = kV + kTile;
+  static constexpr int kDO = kQ + kQStages * kTile;
+  static constexpr int kP = kDO + kQStages * kTile;
+  static constexpr int kDS = kP + 32768;
+  static constexpr int kBar = kDS + 32768;
+  static constexpr int kNumBars = 1 + 2 * kQStages + 4;
+  static constexpr int kTotal = kBar + kNumBars * 8 + 16;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
+  using L = AttnBwdSmem<HD>;
+  constexpr int NS = L::kSlabs;
+  constexpr int QS = L::kQStages;
+  constexpr bool kAliasDQ = HD > 64;  // dQ reuses the S columns when TMEM is full
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* kv_full = &bars[0];
+  uint64_t* q_full = &bars[1];          // [QS]
+  uint64_t* q_empty = &bars[1 + QS];    // [QS]
+  uint64_t* sdp_full = &bars[1 + 2 * QS];
+  uint64_t* pds_full = sdp_full + 1;
+  uint64_t* dq_full = sdp_full + 2;
+  uint64_t* dq_empty = sdp_full + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(&bars[L::kNumBars]);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kvt = blockIdx.x;
+  const int hk = blockIdx.y;
+  const int b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int kv0 = kvt * 128;
+  const int chunk = kv0 / p.chunk_len;
+  const int kv_row0 = kv0 - chunk * p.chunk_len;
+  const int skv_total = p.chunk_len * p.n_chunks;
+  const int n_q_tiles = (p.Sq + 127) / 128;
+  int qt_first = 0;
+  if (kv0 > p.q_pos0) qt_first = (kv0 - p.q_pos0) / 128;
+  const int per_head = n_q_tiles > qt_first ? n_q_tiles - qt_first : 0;
+  const int n_iter = per_head * group;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kSCol = 0, kDPCol = 128, kDVCol = 256, kDKCol = 256 + HD;
+  constexpr uint32_t kDQCol = kAliasDQ ? 0 : 256 + 2 * HD;
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_status(p.status, kBadArgument, 40);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < QS; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 128);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0 && n_iter > 0) {
+      mbar_expect_tx(kv_full, 2 * L::kTile);
+#pragma unroll
+      for (int c = 0; c < NS; ++c) {
+        tma_load_4d(smem + L::kK + c * 16384, &p.k_map[chunk], kv_full, c * 64, kv_row0, hk, b);
+        tma_load_4d(smem + L::kV + c * 16384, &p.v_map[chunk], kv_full, c * 64, kv_row0, hk, b);
+      }
+      for (int i = 0; i < n_iter; ++i) {
+        const int st = i % QS;
+        const int use = i / QS;
+        if (use >= 1 && !mbar_wait(&q_empty[st], (use - 1) & 1, abort_flag, p.status, 41)) break;
+        const int hq = hk * group + i / per_head;
+        const int q0 = (qt_first + i % per_head) * 128;
+        mbar_expect_tx(&q_full[st], 2 * L::kTile);
+#pragma unroll
+        for (int c = 0; c < NS; ++c) {
+          tma_load_4d(smem + L::kQ + st * L::kTile + c * 16384, &p.q_map, &q_full[st], c * 64, q0, hq, b);
+          tma_load_4d(smem + L::kDO + st * L::kTile + c * 16384, &p.do_map, &q_full[st], c * 64, q0, hq, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S, dP
+      constexpr uint32_t idesc_kv = make_idesc_bf16(128, HD, true, true);     // dV, dK
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);    // dQ
+      const uint32_t sK = smem_u32(smem + L::kK);
+      const uint32_t sV = smem_u32(smem + L::kV);
+      const uint32_t sP = smem_u32(smem + L::kP);
+      const uint32_t sDS = smem_u32(smem + L::kDS);
+      auto issue_sdp = [&](int i) {
+        const uint32_t sQ = smem_u32(smem + L::kQ + (i % QS) * L::kTile);
+        const uint32_t sDO = smem_u32(smem + L::kDO + (i % QS) * L::kTile);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          tc_mma_bf16(tmem_base + kSCol, make_smem_desc(sQ + off, 16, 1024),
+                      make_smem_desc(sK + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          tc_mma_bf16(tmem_base + kDPCol, make_smem_desc(sDO + off, 16, 1024),
+                      make_smem_desc(sV + off, 16, 1024), idesc_s, k != 0 ? 1u : 0u);
+        }
+        tc_commit(sdp_full);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, 42) &&
+                mbar_wait(&q_full[0], 0, abort_flag, p.status, 43);
+      if (ok) {
+        tc_fence_after();
+        issue_sdp(0);
+      }
+      for (int i = 0; i < n_iter && ok; ++i) {
+        if (!mbar_wait(pds_full, i & 1, abort_flag, p.status, 44)) break;
+        if (!kAliasDQ && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 45)) break;
+        tc_fence_after();
+        const uint32_t sQ = smem_u32(smem + L::kQ + (i % QS) * L::kTile);
+        const uint32_t sDO = smem_u32(smem + L::kDO + (i % QS) * L::kTile);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dV += P^T dO
+          tc_mma_bf16(tmem_base + kDVCol, make_smem_desc(sP + k * 2048, 16384, 1024),
+                      make_smem_desc(sDO + k * 2048, 16384, 1024), idesc_kv, (i | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dK += dS^T Q
+          tc_mma_bf16(tmem_base + kDKCol, make_smem_desc(sDS + k * 2048, 16384, 1024),
+                      make_smem_desc(sQ + k * 2048, 16384, 1024), idesc_kv, (i | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dQ = dS K
+          tc_mma_bf16(tmem_base + kDQCol,
+                      make_smem_desc(sDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                      make_smem_desc(sK + k * 2048, 16384, 1024), idesc_dq, k != 0 ? 1u : 0u);
+        tc_commit(dq_full);
+        tc_commit(&q_empty[i % QS]);
+        if (i + 1 < n_iter) {
+          const int st = (i + 1) % QS;
+          if (!mbar_wait(&q_full[st], ((i + 1) / QS) & 1, abort_flag, p.status, 46)) break;
+          if (kAliasDQ && !mbar_wait(dq_empty, i & 1, abort_flag, p.status, 47)) break;
+          tc_fence_after();
+          issue_sdp(i + 1);
+        }
+      }
+    }
+  } else {
+    const int r = threadIdx.x;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const float sl2 = p.scale * kLog2e;
+    bool ok = true;
+    for (int i = 0; i < n_iter; ++i) {
+      const int hq = hk * group + i / per_head;
+      const int q0 = (qt_first + i % per_head) * 128;
+      const int q_row = q0 + r;
+      const bool valid = q_row < p.Sq;
+      const long long stat_idx = (static_cast<long long>(b) * p.Hq + hq) * p.Sq + q_row;
+      const float lse2 = valid ? p.lse[stat_idx] * kLog2e : 0.f;
+      const float dlt = valid ? p.delta[stat_idx] : 0.f;
+      int limit = p.q_pos0 + q_row - kv0;
+      if (skv_total - 1 - kv0 < limit) limit = skv_total - 1 - kv0;
+      if (!valid) limit = -1;
+      if (!mbar_wait(sdp_full, i & 1, abort_flag, p.status, 48)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint8_t* sp = smem + L::kP;
+      uint8_t* sds = smem + L::kDS;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sr[32], dpr[32];
+        tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+        tmem_ld_32x32(t_lane + kDPCol + c * 32, dpr);
+        tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) {
+          const bool v0 = c * 32 + jj <= limit;
+          const bool v1 = c * 32 + jj + 1 <= limit;
+          const float p0 = v0 ? exp2f(__uint_as_float(sr[jj]) * sl2 - lse2) : 0.f;
+          const float p1 = v1 ? exp2f(__uint_as_float(sr[jj + 1]) * sl2 - lse2) : 0.f;
+          const float d0 = p0 * (__uint_as_float(dpr[jj]) - dlt) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dpr[jj + 1]) - dlt) * p.scale;
+          pp[jj / 2] = pack_bf16x2(p0, p1);
+          dd[jj / 2] = pack_bf16x2(d0, d1);
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const uint32_t off = (c >> 1) * 16384 + swz128_offset(r, (c & 1) * 4 + t);
+          *reinterpret_cast<uint4*>(sp + off) = make_uint4(pp[t * 4], pp[t * 4 + 1], pp[t * 4 + 2], pp[t * 4 + 3]);
+          *reinterpret_cast<uint4*>(sds + off) = make_uint4(dd[t * 4], dd[t * 4 + 1], dd[t * 4 + 2], dd[t * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+      if (!mbar_wait(dq_full, i & 1, abort_flag, p.status, 49)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float* dq_row = p.dq_acc + ((static_cast<long long>(b) * p.Sq + q_row) * p.Hq + hq) * p.d;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t qr[32];
+        tmem_ld_32x32(t_lane + kDQCol + c * 32, qr);
+        tmem_ld_wait();
+        if (valid && c * 32 < p.d) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) atomicAdd(dq_row + c * 32 + jj, __uint_as_float(qr[jj]));
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+    }
+    // dK / dV of this tile: the last dq_full also covers their MMAs.
+    const int kv_row = kv_row0 + r;
+    if (ok && kv_row < p.chunk_len) {
+      // (when n_iter == 0 nothing was accumulated: write zeros)
+      const long long off = b * p.dkv_stride_b + static_cast<long long>(kv_row) * p.dkv_stride_s +
+                            hk * p.dkv_stride_h;
+      __nv_bfloat16* dk_row = p.dk[chunk] + off;
+      __nv_bfloat16* dv_row = p.dv[chunk] + off;
+      if (n_iter == 0) {
+        for (int c = 0; c < p.d; c += 8) {
+          *reinterpret_cast<uint4*>(dk_row + c) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(dv_row + c) = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+    if (ok && n_iter > 0) {
+      const long long off = b * p.dkv_stride_b + static_cast<long long>(kv_row) * p.dkv_stride_s +
+                            hk * p.dkv_stride_h;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* row = (which == 0 ? p.dv[chunk] : p.dk[chunk]) + off;
+        const uint32_t col = which == 0 ? kDVCol : kDKCol;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t ar[32];
+          tmem_ld_32x32(t_lane + col + c * 32, ar);
+          tmem_ld_wait();
+          if (kv_row < p.chunk_len && c * 32 < p.d) {
+            uint4* dst = reinterpret_cast<uint4*>(row + c * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack_bf16x2(__uint_as_float(ar[q * 8 + 0]), __uint_as_float(ar[q * 8 + 1]));
+              u.y = pack_bf16x2(__uint_as_float(ar[q * 8 + 2]), __uint_as_float(ar[q * 8 + 3]));
+              u.z = pack_bf16x2(__uint_as_float(ar[q * 8 + 4]), __uint_as_float(ar[q * 8 + 5]));
+              u.w = pack_bf16x2(__uint_as_float(ar[q * 8 + 6]), __uint_as_float(ar[q * 8 + 7]));
+              dst[q] = u;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// delta[b,h,s] = sum_d dO * O ; also clears the fp32 dQ accumulator.
+__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dO,
+                                     long long o_sb, long long o_ss, long long o_sh, long long do_sb,
+                                     long long do_ss, long long do_sh, float* __restrict__ delta,
+                                     float* __restrict__ dq_acc, int B, int H, int S, int d) {
+  // one warp per (b, s, h) row
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * S * H;
+  if (row >= total) return;
+  const int h = row % H;
+  const long long bs = row / H;
+  const int s = bs % S;
+  const int b = bs / S;
+  const __nv_bfloat16* orow = o + b * o_sb + s * o_ss + h * o_sh;
+  const __nv_bfloat16* drow = dO + b * do_sb + s * do_ss + h * do_sh;
+  float acc = 0.f;
+  for (int c = lane * 2; c < d; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(orow + c));
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(drow + c));
+    acc += a.x * g.x + a.y * g.y;
+  }
+#pragma unroll
+  for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
+  float* dq = dq_acc + row * d;
+  for (int c = lane; c < d; c += 32) dq[c] = 0.f;
+}
+
+__global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dq,
+                                     long long dq_sb, long long dq_ss, long long dq_sh, int B, int H,
+                                     int S, int d) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;  // pair index
+  const long long total = static_cast<long long>(B) * S * H * d / 2;
+  if (idx >= total) return;
+  const long long e = idx * 2;
+  const int c = e % d;
+  const long long row = e / d;
+  const int h = row % H;
+  const long long bs = row / H;
+  const int s = bs % S;
+  const int b = bs / S;
+  const float2 v = *reinterpret_cast<const float2*>(dq_acc + e);
+  *reinterpret_cast<__nv_bfloat162*>(dq + b * dq_sb + s * dq_ss + h * dq_sh + c) = __floats2bfloat162_rn(v.x, v.y);
+}
+
+static int make_attn_map(CUtensorMap* m, const void* ptr, int d, int S, int H, int B, long long ss,
+                         long long sh, long long sb) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(d), static_cast<uint64_t>(S), static_cast<uint64_t>(H),
+                            static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(ss) * 2, static_cast<uint64_t>(sh) * 2,
+                               static_cast<uint64_t>(sb) * 2};
+  const uint32_t box[4] = {64, 128, 1, 1};
+  return make_tmap_bf16(m, ptr, 4, dims, strides, box);
+}
+
+}  // namespace nmb
+
+using namespace nmb;
+
+// Tensor descriptor passed from Python: pointer + element strides of the
+// (batch, seq, head) dimensions; head_dim is contiguous.
+struct NmbTensor4 {
+  void* ptr;
+  long long stride_b, stride_s, stride_h;
+};
+
+extern "C" int nmb_attn_fwd(const NmbTensor4* q, const NmbTensor4* k_chunks, const NmbTensor4* v_chunks,
+                            int n_chunks, int chunk_len, const NmbTensor4* o, float* lse, int B, int Hq,
+                            int Hkv, int Sq, int d, int q_pos0, float scale, int* status, void* stream) {
+  if (n_chunks < 1 || n_chunks > kMaxChunks) return kBadArgument;
+  if (d != 64 && d != 96 && d != 128) return kBadArgument;
+  if (n_chunks > 1 && (chunk_len % 128) != 0) return kBadArgument;
+  AttnFwdParams p;
+  if (make_attn_map(&p.q_map, q->ptr, d, Sq, Hq, B, q->stride_s, q->stride_h, q->stride_b)) return 101;
+  for (int c = 0; c < n_chunks; ++c) {
+    if (make_attn_map(&p.k_map[c], k_chunks[c].ptr, d, chunk_len, Hkv, B, k_chunks[c].stride_s,
+                      k_chunks[c].stride_h, k_chunks[c].stride_b))
+      return 102;
+    if (make_attn_map(&p.v_map[c], v_chunks[c].ptr, d, chunk_len, Hkv, B, v_chunks[c].stride_s,
+                      v_chunks[c].stride_h, v_chunks[c].stride_b))
+      return 103;
+  }
+  p.o = static_cast<__nv_bfloat16*>(o->ptr);
+  p.o_stride_b = o->stride_b;
+  p.o_stride_s = o->stride_s;
+  p.o_stride_h = o->stride_h;
+  p.lse = lse;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq;
+  p.chunk_len = chunk_len; p.n_chunks = n_chunks;
+  p.d = d; p.q_pos0 = q_pos0; p.scale = scale; p.status = status;
+  dim3 grid((Sq + 127) / 128, Hq, B);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (d == 64) {
+    static bool cfg = false;
+    if (!cfg) {
+      e = cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnFwdSmem<64>::kTotal);
+      if (e != cudaSuccess) return 300 + e;
+      cfg = true;
+    }
+    attn_fwd_kernel<64><<<grid, kAttnThreads, AttnFwdSmem<64>::kTotal, s>>>(p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) {
+      e = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnFwdSmem<128>::kTotal);
+      if (e != cudaSuccess) return 300 + e;
+      cfg = true;
+    }
+    attn_fwd_kernel<128><<<grid, kAttnThreads, AttnFwdSmem<128>::kTotal, s>>>(p);
+  }
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+// dq_acc: fp32 scratch [B, Sq, Hq, d]; delta: fp32 scratch [B, Hq, Sq].
+extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, const NmbTensor4* v_chunks,
+                            int n_chunks, int chunk_len, const NmbTensor4* o, const NmbTensor4* dout,
+                            const float* lse, float* delta, float* dq_acc, const NmbTensor4* dq,
+                            const NmbTensor4* dk_chunks, const NmbTensor4* dv_chunks, int B, int Hq, int Hkv,
+                            int Sq, int d, int q_pos0, int n_visible_kv_tiles, float scale, int* status,
+                            void* stream) {
+  if (n_chunks < 1 || n_chunks > kMaxChunks) return kBadArgument;
+  if (d != 64 && d != 96 && d != 128) return kBadArgument;
+  if (n_chunks > 1 && (chunk_len % 128) != 0) return kBadArgument;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  {
+    const long long rows = static_cast<long long>(B) * Sq * Hq;
+    const int threads = 256;
+    const long long blocks = (rows * 32 + threads - 1) / threads;
+    attn_bwd_prep_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(o->ptr), static_cast<const __nv_bfloat16*>(dout->ptr), o->stride_b,
+        o->stride_s, o->stride_h, dout->stride_b, dout->stride_s, dout->stride_h, delta, dq_acc, B, Hq, Sq, d);
+  }
+  AttnBwdParams p;
+  if (make_attn_map(&p.q_map, q->ptr, d, Sq, Hq, B, q->stride_s, q->stride_h, q->stride_b)) return 101;
+  if (make_attn_map(&p.do_map, dout->ptr, d, Sq, Hq, B, dout->stride_s, dout->stride_h, dout->stride_b)) return 104;
+  for (int c = 0; c < n_chunks; ++c) {
+    if (make_attn_map(&p.k_map[c], k_chunks[c].ptr, d, chunk_len, Hkv, B, k_chunks[c].stride_s,
+                      k_chunks[c].stride_h, k_chunks[c].stride_b))
+      return 102;
+    if (make_attn_map(&p.v_map[c], v_chunks[c].ptr, d, chunk_len, Hkv, B, v_chunks[c].stride_s,
+                      v_chunks[c].stride_h, v_chunks[c].stride_b))
+      return 103;
+    p.dk[c] = static_cast<__nv_bfloat16*>(dk_chunks[c].ptr);
+    p.dv[c] = static_cast<__nv_bfloat16*>(dv_chunks[c].ptr);
+  }
+  p.dkv_stride_b = dk_chunks[0].stride_b;
+  p.dkv_stride_s = dk_chunks[0].stride_s;
+  p.dkv_stride_h = dk_chunks[0].stride_h;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq;
+  p.chunk_len = chunk_len; p.n_chunks = n_chunks;
+  p.d = d; p.q_pos0 = q_pos0; p.scale = scale; p.status = status;
+  dim3 grid(n_visible_kv_tiles, Hkv, B);
+  cudaError_t e;
+  if (d == 64) {
+    static bool cfg = false;
+    if (!cfg) {
+      e = cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem<64>::kTotal);
+      if (e != cudaSuccess) return 300 + e;
+      cfg = true;
+    }
+    attn_bwd_kernel<64><<<grid, kAttnThreads, AttnBwdSmem<64>::kTotal, s>>>(p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) {
+      e = cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem<128>::kTotal);
+      if (e != cudaSuccess) return 300 + e;
+      cfg = true;
+    }
+    attn_bwd_kernel<128><<<grid, kAttnThreads, AttnBwdSmem<128>::kTotal, s>>>(p);
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return 400 + e;
+  {
+    const long long pairs = static_cast<long long>(B) * Sq * Hq * d / 2;
+    const int threads = 256;
+    attn_dq_store_kernel<<<static_cast<unsigned>((pairs + threads - 1) / threads), threads, 0, s>>>(
+        dq_acc, static_cast<__nv_bfloat16*>(dq->ptr), dq->stride_b, dq->stride_s, dq->stride_h, B, Hq, Sq, d);
+  }
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 500 + e;
+}

@@ -1,0 +1,109 @@
+"""Causal flash attention (``csrc/attention_tcgen05.cu``) as an autograd op.
+
+Tensors are ``[B, S, heads, d]`` *views* with a contiguous last dimension and
+arbitrary other strides, so the packed output of a fused QKV projection is
+consumed in place.  The key/value side may be given as a list of chunks (one
+per context-parallel rank, possibly peer-memory tensors); chunk ``c`` covers
+global key positions ``[c*chunk_len, (c+1)*chunk_len)`` and the query rows
+start at global position ``q_pos0``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import native
+
+
+class _Tensor4(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("stride_b", ctypes.c_longlong),
+                ("stride_s", ctypes.c_longlong), ("stride_h", ctypes.c_longlong)]
+
+
+def _desc(t: torch.Tensor) -> _Tensor4:
+    assert t.dim() == 4 and t.stride(3) == 1 and t.dtype == torch.bfloat16
+    assert t.data_ptr() % 16 == 0 and all(s % 8 == 0 for s in t.stride()[:3] if s != 0)
+    return _Tensor4(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+
+
+def _desc_array(ts: Sequence[torch.Tensor]):
+    arr = (_Tensor4 * len(ts))()
+    for i, t in enumerate(ts):
+        arr[i] = _desc(t)
+    return arr
+
+
+def _visible_kv_tiles(sq: int, q_pos0: int, skv_total: int) -> int:
+    last = q_pos0 + sq - 1
+    return min((last + 128) // 128, (skv_total + 127) // 128)
+
+
+def attn_fwd(q, k_chunks, v_chunks, scale: float, q_pos0: int = 0):
+    b, sq, hq, d = q.shape
+    chunk_len, hkv = k_chunks[0].shape[1], k_chunks[0].shape[2]
+    out = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+    qd, od = _desc(q), _desc(out)
+    rc = native.lib().nmb_attn_fwd(
+        ctypes.byref(qd), _desc_array(k_chunks), _desc_array(v_chunks), ctypes.c_int(len(k_chunks)),
+        ctypes.c_int(chunk_len), ctypes.byref(od), native.ptr(lse), ctypes.c_int(b), ctypes.c_int(hq),
+        ctypes.c_int(hkv), ctypes.c_int(sq), ctypes.c_int(d), ctypes.c_int(q_pos0),
+        ctypes.c_float(scale), native.ptr(native.status_word(q.device)), native.stream_ptr(q.device))
+    native.check_rc(rc, "nmb_attn_fwd")
+    return out, lse
+
+
+def attn_bwd(q, k_chunks, v_chunks, out, dout, lse, scale: float, q_pos0: int = 0,
+             dk_chunks: Optional[Sequence[torch.Tensor]] = None,
+             dv_chunks: Optional[Sequence[torch.Tensor]] = None):
+    """Returns ``(dq, dk_chunks, dv_chunks)``.  ``dk_chunks[c]`` receives this
+    rank's contribution to chunk ``c``; rows of chunks the queries cannot see
+    are left untouched (callers pass zero-filled or freshly visible buffers)."""
+    b, sq, hq, d = q.shape
+    chunk_len, hkv = k_chunks[0].shape[1], k_chunks[0].shape[2]
+    n_chunks = len(k_chunks)
+    if dout.stride(3) != 1:
+        dout = dout.contiguous()
+    dq = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device)
+    if dk_chunks is None:
+        dk_chunks = [torch.zeros((b, chunk_len, hkv, d), dtype=torch.bfloat16, device=q.device) for _ in range(n_chunks)]
+        dv_chunks = [torch.zeros_like(t) for t in dk_chunks]
+    delta = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+    dq_acc = torch.empty((b, sq, hq, d), dtype=torch.float32, device=q.device)
+    n_tiles = _visible_kv_tiles(sq, q_pos0, chunk_len * n_chunks)
+    qd, od, dod, dqd = _desc(q), _desc(out), _desc(dout), _desc(dq)
+    rc = native.lib().nmb_attn_bwd(
+        ctypes.byref(qd), _desc_array(k_chunks), _desc_array(v_chunks), ctypes.c_int(n_chunks),
+        ctypes.c_int(chunk_len), ctypes.byref(od), ctypes.byref(dod), native.ptr(lse), native.ptr(delta),
+        native.ptr(dq_acc), ctypes.byref(dqd), _desc_array(dk_chunks), _desc_array(dv_chunks),
+        ctypes.c_int(b), ctypes.c_int(hq), ctypes.c_int(hkv), ctypes.c_int(sq), ctypes.c_int(d),
+        ctypes.c_int(q_pos0), ctypes.c_int(n_tiles), ctypes.c_float(scale),
+        native.ptr(native.status_word(q.device)), native.stream_ptr(q.device))
+    native.check_rc(rc, "nmb_attn_bwd")
+    return dq, list(dk_chunks), list(dv_chunks)
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        out, lse = attn_fwd(q, [k], [v], scale, 0)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = attn_bwd(q, [k], [v], out, dout, lse, ctx.scale, 0)
+        return dq, dk[0], dv[0], None
+
+
+def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
+    """Causal attention over ``[B, S, heads, d]`` views; returns ``[B, S, Hq, d]``."""
+    return _FlashAttention.apply(q, k, v, float(scale))
+
+
+def attention_supported(d: int) -> bool:
+    return d in (64, 96, 128)
