@@ -58,3 +58,11 @@ class TorchDistBackend:
 
     def barrier(self, *, group: Optional[Any] = None) -> None:
         dist.barrier(group=group)
+
+    # Extras beyond the eight-method protocol: non-blocking point-to-point, used
+    # by the pipeline schedule so a send does not stall the compute stream.
+    def isend(self, tensor: Tensor, dst: int, *, group: Optional[Any] = None) -> Any:
+        return dist.isend(tensor, dst, group=group)
+
+    def irecv(self, tensor: Tensor, src: int, *, group: Optional[Any] = None) -> Any:
+        return dist.irecv(tensor, src, group=group)

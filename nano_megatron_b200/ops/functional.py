@@ -1,0 +1,313 @@
+"""Autograd-level ops used by the parallel layers and models.
+
+Every function has two implementations behind one name:
+
+* CUDA + bf16 tensors  -> the sm_100a kernels of this package (tcgen05 GEMM
+  with fused epilogues, fused norm / CE / embedding kernels), with hand-written
+  backward passes;
+* anything else (CPU, fp32) -> the plain PyTorch expression of the same maths,
+  which is what the oracle and the Gloo tests run.
+
+There is no third path and no silent fallback on a GPU: bf16 CUDA tensors
+always go to the native kernels (a missing library raises).
+
+Gradient buffers.  A parameter may carry ``main_grad`` -- a persistent tensor
+of its own shape (a view into a DDP bucket or a model-wide flat buffer).  The
+weight-gradient GEMM, the bias reduction and the embedding scatter then
+accumulate straight into it, return no gradient to autograd, and announce
+completion through ``param._nmb_grad_ready()`` when that attribute exists.
+"""
+from __future__ import annotations
+
+from typing import Any, Optional
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from . import kernels
+from .gemm import EPI_GELU, EPI_PLAIN, gemm_bf16, gemm_supported
+
+
+def use_native(t: Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16
+
+
+def _deliver_grad(param: Optional[Tensor], compute, *, shape_like: Optional[Tensor] = None):
+    """Run ``compute(out, accumulate)``; returns the grad for autograd or None
+    when it was accumulated into ``param.main_grad``."""
+    main = getattr(param, "main_grad", None) if param is not None else None
+    if main is not None:
+        compute(main, True)
+        ready = getattr(param, "_nmb_grad_ready", None)
+        if ready is not None:
+            ready()
+        return None
+    return compute(None, False)
+
+
+# ------------------------------------------------------------------ linear --
+class _LinearFn(torch.autograd.Function):
+    """y = act(x W^T + b) (+ residual) on the tcgen05 GEMM."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor], gelu: bool):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1 or (x2.stride(0) % 8) != 0:
+            x2 = x2.contiguous()
+        n = weight.shape[0]
+        res2 = residual.reshape(-1, n) if residual is not None else None
+        pre = None
+        if gelu:
+            pre = torch.empty((x2.shape[0], n), dtype=torch.bfloat16, device=x.device)
+            y = gemm_bf16(x2, weight, bias=bias, mode=EPI_GELU, aux_out=pre)
+        else:
+            y = gemm_bf16(x2, weight, bias=bias, residual=res2, mode=EPI_PLAIN)
+        ctx.save_for_backward(x2, weight, pre)
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.params = (weight, bias)
+        ctx.in_shape = x.shape
+        return y.view(*x.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        x2, weight, pre = ctx.saved_tensors
+        w_param, b_param = ctx.params
+        n = weight.shape[0]
+        dy2 = dy.reshape(-1, n)
+        if dy2.stride(-1) != 1 or (dy2.stride(0) % 8) != 0:
+            dy2 = dy2.contiguous()
+        d_res = dy if ctx.has_res else None
+        dz = kernels.gelu_bwd(pre, dy2) if pre is not None else dy2
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_bf16(dz, weight, b_mn=True).view(ctx.in_shape)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = _deliver_grad(
+                w_param,
+                lambda out, acc: gemm_bf16(dz, x2, a_mn=True, b_mn=True, out=out, accumulate=acc),
+            )
+        db = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dz, out=out, accumulate=acc))
+        return dx, dw, db, d_res, None
+
+
+def _native_linear_ok(x: Tensor, weight: Tensor) -> bool:
+    k = x.shape[-1]
+    n = weight.shape[0]
+    return use_native(x) and weight.dtype == torch.bfloat16 and weight.is_contiguous() and \
+        gemm_supported(k, k, k, n) and n % 8 == 0
+
+
+def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, *, residual: Optional[Tensor] = None,
+           gelu: bool = False) -> Tensor:
+    """``act(x @ weight.T + bias) + residual`` (``gelu`` and ``residual`` are exclusive)."""
+    assert not (gelu and residual is not None)
+    if _native_linear_ok(x, weight):
+        return _LinearFn.apply(x, weight, bias, residual, gelu)
+    # Rows that are not multiples of 16 bytes cannot be described to TMA; such
+    # (toy) shapes use the PyTorch expression below.
+    y = F.linear(x, weight, bias)
+    if gelu:
+        from ..reference.layers import gelu_erf
+        y = gelu_erf(y)
+    if residual is not None:
+        y = residual + y
+    return y
+
+
+# -------------------------------------------------------------------- norm --
+class _NormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], eps: float, rms: bool):
+        y, mean, rstd = kernels.norm_fwd(x, weight, bias, eps, rms)
+        ctx.save_for_backward(x, weight, mean, rstd)
+        ctx.rms = rms
+        ctx.params = (weight, bias)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        x, weight, mean, rstd = ctx.saved_tensors
+        w_param, b_param = ctx.params
+        dx, dw, db = kernels.norm_bwd(dy, x, weight, mean, rstd, ctx.rms, want_bias=b_param is not None and not ctx.rms)
+        return dx, dw, db, None, None
+
+
+def layer_norm(x: Tensor, weight: Tensor, bias: Optional[Tensor], eps: float) -> Tensor:
+    if use_native(x) and x.shape[-1] % 2 == 0:
+        return _NormFn.apply(x, weight, bias, eps, False)
+    return F.layer_norm(x, (x.shape[-1],), weight=weight, bias=bias, eps=eps)
+
+
+def rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
+    if use_native(x) and x.shape[-1] % 2 == 0:
+        return _NormFn.apply(x, weight, None, eps, True)
+    from ..reference.layers import rms_norm as _rms
+    return _rms(x, weight, eps)
+
+
+# ------------------------------------------------------------- activations --
+class _GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return kernels.gelu_fwd(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return kernels.gelu_bwd(x, dy)
+
+
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return kernels.swiglu_fwd(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        return kernels.swiglu_bwd(x, dy)
+
+
+def gelu(x: Tensor) -> Tensor:
+    if use_native(x) and x.numel() % 2 == 0:
+        return _GeluFn.apply(x)
+    from ..reference.layers import gelu_erf
+    return gelu_erf(x)
+
+
+def swiglu(x: Tensor) -> Tensor:
+    if use_native(x) and (x.shape[-1] // 2) % 2 == 0:
+        return _SwigluFn.apply(x)
+    from ..reference.layers import swiglu as _sw
+    return _sw(x)
+
+
+class _RopeFn(torch.autograd.Function):
+    """Rotates q and k in place inside the packed projection output."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, positions: Tensor, inv_freq: Tensor):
+        out = x.clone()
+        kernels.rope_inplace(out, positions, inv_freq, 1.0)
+        ctx.save_for_backward(positions, inv_freq)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        positions, inv_freq = ctx.saved_tensors
+        dx = dy.clone()
+        kernels.rope_inplace(dx, positions, inv_freq, -1.0)
+        return dx, None, None
+
+
+def rope_bshd(x: Tensor, positions: Tensor, inv_freq: Tensor) -> Tensor:
+    """Rotary embedding on a ``[B, S, heads, d]`` bf16 CUDA tensor (interleaved pairs)."""
+    return _RopeFn.apply(x, positions.contiguous(), inv_freq)
+
+
+# --------------------------------------------------------------- embedding --
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids: Tensor, positions: Optional[Tensor], tok_w: Tensor, pos_w: Optional[Tensor],
+                vocab_start: int):
+        ids = ids.contiguous()
+        if positions is not None:
+            positions = positions.contiguous()
+        out = kernels.embedding_fwd(ids, positions, tok_w, pos_w, vocab_start)
+        ctx.save_for_backward(ids, positions)
+        ctx.params = (tok_w, pos_w)
+        ctx.vocab_start = vocab_start
+        return out
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        ids, positions = ctx.saved_tensors
+        tok_w, pos_w = ctx.params
+        dy = dy.contiguous()
+        results = {}
+
+        def run(tok_out, pos_out):
+            kernels.embedding_bwd(ids, positions, dy, tok_out, pos_out, ctx.vocab_start)
+
+        tok_main = getattr(tok_w, "main_grad", None)
+        pos_main = getattr(pos_w, "main_grad", None) if pos_w is not None else None
+        d_tok = tok_main if tok_main is not None else torch.zeros_like(tok_w)
+        d_pos = None
+        if pos_w is not None:
+            d_pos = pos_main if pos_main is not None else torch.zeros_like(pos_w)
+        run(d_tok, d_pos)
+        for param, main in ((tok_w, tok_main), (pos_w, pos_main)):
+            if param is not None and main is not None:
+                ready = getattr(param, "_nmb_grad_ready", None)
+                if ready is not None:
+                    ready()
+        return (None, None, None if tok_main is not None else d_tok,
+                None if (pos_w is None or pos_main is not None) else d_pos, None)
+
+
+def embedding(ids: Tensor, positions: Optional[Tensor], tok_w: Tensor, pos_w: Optional[Tensor],
+              vocab_start: int = 0) -> Tensor:
+    """``tok_w[ids - vocab_start]`` (zero rows for ids outside the shard) ``+ pos_w[positions]``."""
+    if use_native(tok_w) and tok_w.shape[1] % 2 == 0:
+        return _EmbeddingFn.apply(ids, positions if pos_w is not None else None, tok_w, pos_w, vocab_start)
+    vloc = tok_w.shape[0]
+    outside = (ids < vocab_start) | (ids >= vocab_start + vloc)
+    local = (ids - vocab_start).masked_fill(outside, 0)
+    out = F.embedding(local, tok_w).masked_fill(outside.unsqueeze(-1), 0.0)
+    if pos_w is not None:
+        out = out + F.embedding(positions, pos_w)
+    return out
+
+
+# ----------------------------------------------------------- cross entropy --
+class _CrossEntropyFn(torch.autograd.Function):
+    """Sum of token losses and number of valid tokens over vocabulary-sharded logits."""
+
+    @staticmethod
+    def forward(ctx, logits: Tensor, target: Tensor, vocab_start: int, ignore_index: int, group: Any,
+                backend: Any, tp_size: int, inplace_backward: bool):
+        target = target.contiguous()
+        stats = kernels.ce_stats(logits, target, vocab_start)
+        if tp_size > 1:
+            gathered = torch.empty((tp_size, *stats.shape), dtype=stats.dtype, device=stats.device)
+            backend.all_gather_into_tensor(gathered.view(-1, stats.shape[-1]), stats, group=group)
+        else:
+            gathered = stats.unsqueeze(0)
+        lse, accum, _ = kernels.ce_combine(gathered, target, ignore_index)
+        ctx.save_for_backward(logits, target, lse)
+        ctx.meta = (vocab_start, ignore_index, inplace_backward)
+        loss_sum, count = accum[0], accum[1]
+        ctx.mark_non_differentiable(count)
+        return loss_sum, count
+
+    @staticmethod
+    def backward(ctx, g_sum: Tensor, _g_count):
+        logits, target, lse = ctx.saved_tensors
+        vocab_start, ignore_index, inplace = ctx.meta
+        gscale = g_sum.to(torch.float32).reshape(1).contiguous()
+        dlogits = kernels.ce_bwd(logits, target, vocab_start, ignore_index, lse, gscale,
+                                 out=logits if inplace else None)
+        return dlogits, None, None, None, None, None, None, None
+
+
+def cross_entropy_sum(logits2d: Tensor, target1d: Tensor, *, vocab_start: int = 0, ignore_index: int = -100,
+                      group: Any = None, backend: Any = None, tp_size: int = 1,
+                      inplace_backward: bool = False) -> tuple[Tensor, Tensor]:
+    """Returns ``(sum of per-token losses, number of non-ignored tokens)`` as fp32 scalars.
+
+    ``logits2d`` is ``[N, V/tp]`` (this rank's vocabulary shard starting at
+    ``vocab_start``); one all-gather of three floats per token replaces the
+    three all-reduces of the reference.  bf16 CUDA only.
+    """
+    assert use_native(logits2d)
+    if logits2d.stride(-1) != 1:
+        logits2d = logits2d.contiguous()
+    return _CrossEntropyFn.apply(logits2d, target1d, vocab_start, ignore_index, group, backend, tp_size,
+                                 inplace_backward)
