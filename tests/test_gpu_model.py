@@ -1,0 +1,105 @@
+"""The bf16 GPU model (all native kernels) against the fp32 CPU oracle."""
+from __future__ import annotations
+
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture
+def ctx(monkeypatch, request):
+    import nano_megatron_b200.parallel as P
+    from tests._dist_utils import port_for
+    monkeypatch.setenv("MASTER_ADDR", "127.0.0.1")
+    monkeypatch.setenv("MASTER_PORT", str(port_for(request.node.nodeid)))
+    monkeypatch.setenv("RANK", "0")
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    monkeypatch.setenv("LOCAL_RANK", "0")
+    c = P.initialize_parallel(P.ParallelConfig(), dist_backend="nccl")
+    yield c
+    P.destroy_parallel()
+
+
+KNOBS = {
+    "gpt2": dict(position_embedding_type="learned_absolute", gated_linear_unit=False, use_bias=True,
+                 tie_word_embeddings=True, use_fused_qkv=True),
+    "rope_swiglu_gqa": dict(num_query_groups=2, use_fused_qkv=True),
+    "separate_qkv_rms": dict(normalization="rmsnorm", use_bias=True),
+}
+
+
+@pytest.mark.parametrize("name", list(KNOBS))
+def test_bf16_model_tracks_fp32_oracle(ctx, name):
+    from nano_megatron_b200.models import build_tp_gpt_from_reference
+    from nano_megatron_b200.ops import native
+    from nano_megatron_b200.reference import ReferenceGPT, ReferenceGPTConfig, seed_all, shifted_cross_entropy
+
+    seed_all(0)
+    cfg = ReferenceGPTConfig(num_layers=2, hidden_size=256, num_heads=4, vocab_size=512, max_seq_len=256,
+                             **KNOBS[name])
+    ref = ReferenceGPT(cfg)
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() > 1:
+                p.mul_(0.5)
+    model = build_tp_gpt_from_reference(ref, ctx).to("cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, cfg.vocab_size, (2, 256))
+    logits = model(ids.cuda())
+    loss = model.shifted_cross_entropy(logits, ids.cuda())
+    loss.backward()
+    torch.cuda.synchronize()
+    native.check_status()
+    cfg_cpu = ReferenceGPTConfig(**{**cfg.__dict__, "attn_backend": "unfused"})
+    ref.config = cfg_cpu
+    for blk in ref.blocks:
+        blk.attn.config = cfg_cpu
+    ref_logits = ref(ids)
+    ref_loss = shifted_cross_entropy(ref_logits, ids)
+    ref_loss.backward()
+    scale = ref_logits.abs().max().item()
+    assert (logits.float().cpu() - ref_logits).abs().max().item() < 4e-2 * scale
+    assert abs(loss.item() - ref_loss.item()) < 3e-2 * abs(ref_loss.item())
+    ref_grads = dict(ref.named_parameters())
+    worst = 0.0
+    for n, p in model.named_parameters():
+        if cfg.normalization == "rmsnorm" and n.endswith("_bias") and "ln" in n:
+            continue
+        g, r = p.grad.float().cpu(), ref_grads[n].grad
+        rel = (g - r).norm().item() / (r.norm().item() + 1e-6)
+        worst = max(worst, rel)
+        assert rel < 8e-2, (n, rel)
+
+
+def test_training_loss_decreases_and_matches_oracle_trajectory(ctx):
+    from nano_megatron_b200.models import build_tp_gpt_from_reference
+    from nano_megatron_b200.reference import AdamW, ReferenceGPT, gpt_preset, seed_all, shifted_cross_entropy
+
+    seed_all(0)
+    cfg = gpt_preset("small", attn_backend="auto")
+    ref = ReferenceGPT(cfg)
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() > 1:
+                p.normal_(0, 0.02)
+    model = build_tp_gpt_from_reference(ref, ctx).to("cuda", dtype=torch.bfloat16)
+    opt = AdamW(model.named_parameters(), lr=1e-3, weight_decay=0.01)
+    cpu_opt = AdamW(ref.named_parameters(), lr=1e-3, weight_decay=0.01)
+    ids = torch.randint(0, cfg.vocab_size, (4, 256))
+    gpu_losses, cpu_losses = [], []
+    for _ in range(6):
+        opt.zero_grad()
+        loss = model.shifted_cross_entropy(model(ids.cuda()), ids.cuda())
+        loss.backward()
+        opt.step()
+        gpu_losses.append(loss.item())
+        cpu_opt.zero_grad()
+        l2 = shifted_cross_entropy(ref(ids), ids)
+        l2.backward()
+        cpu_opt.step()
+        cpu_losses.append(l2.item())
+    assert gpu_losses[-1] < gpu_losses[0]
+    for a, b in zip(gpu_losses, cpu_losses):
+        assert abs(a - b) < 5e-2 * abs(b), (gpu_losses, cpu_losses)
