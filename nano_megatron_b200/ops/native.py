@@ -85,6 +85,14 @@ def check_status(device: torch.device | None = None, *, reset: bool = True) -> N
         )
 
 
+#: kernels launched by each C entry point (for launch accounting)
+_KERNELS_PER_CALL = {"nmb_attn_bwd": 3, "nmb_col_reduce": 2, "nmb_adamw_step": 2}
+#: running count of kernels of this library launched (or captured) by this process
+launches = 0
+
+
 def check_rc(rc: int, what: str) -> None:
+    global launches
     if rc != 0:
         raise NativeKernelError(f"{what}: launcher returned {rc}")
+    launches += _KERNELS_PER_CALL.get(what, 1)

@@ -96,6 +96,7 @@ class AdamW:
         if self._fused is None or self._fused.key != key:
             states = [self._ensure_state(n, p) for n, p in live]
             self._fused = FusedAdamWPlan(key, [p for _, p in live], states)
+            self._fused.names = [n for n, _ in live]
         self._fused.step(self.lr, self.betas, self.eps, self.weight_decay)
         for n, _ in live:
             # `step` is mirrored on the host so state_dict() needs no sync.
@@ -112,7 +113,15 @@ class AdamW:
                 p.grad.zero_()
 
     # ---------------------------------------------------------- state dict --
+    def _sync_step_from_device(self) -> None:
+        """A replayed CUDA graph advances the device step counter only."""
+        if self._fused is not None:
+            done = int(self._fused.step_count.item())
+            for n in self._fused.names:
+                self.state[n]["step"] = done
+
     def state_dict(self) -> dict[str, dict[str, Any]]:
+        self._sync_step_from_device()
         return {
             n: {"exp_avg": s["exp_avg"].clone(), "exp_avg_sq": s["exp_avg_sq"].clone(), "step": int(s["step"])}
             for n, s in self.state.items()
