@@ -43,20 +43,68 @@ __global__ void adamw_kernel(const AdamTensor* __restrict__ table, int n_tensors
   const float step_size = lr / corr1;
   const float inv_sqrt_corr2 = 1.f / sqrtf(corr2);
   const float decay = 1.f - lr * wd;
-  for (int i = threadIdx.x; i < kAdamBlockElems; i += kAdamThreads) {
+  auto update = [&](float g, float& w, float& m, float& v) {
+    if (wd != 0.f) w *= decay;
+    m = m * b1 + g * (1.f - b1);
+    v = v * b2 + g * g * (1.f - b2);
+    const float denom = sqrtf(v) * inv_sqrt_corr2 + eps;
+    w -= step_size * (m / denom);
+  };
+  const long long remaining = t.numel - base;
+  const int count = remaining < kAdamBlockElems ? static_cast<int>(remaining) : kAdamBlockElems;
+  const uintptr_t align_bits = reinterpret_cast<uintptr_t>(t.param) | reinterpret_cast<uintptr_t>(t.grad) |
+                               reinterpret_cast<uintptr_t>(t.exp_avg) | reinterpret_cast<uintptr_t>(t.exp_avg_sq);
+  const bool vec = t.param_bf16 && t.grad_bf16 && (align_bits & 15) == 0 && (base % 8) == 0;
+  int done = 0;
+  if (vec) {
+    // 8 elements per thread per trip: one 16-byte load of param and grad, two of each moment.
+    const int groups = count / 8;
+    __nv_bfloat16* pw = static_cast<__nv_bfloat16*>(t.param) + base;
+    const __nv_bfloat16* pg = static_cast<const __nv_bfloat16*>(t.grad) + base;
+    float* pm = t.exp_avg + base;
+    float* pv = t.exp_avg_sq + base;
+    for (int gi = threadIdx.x; gi < groups; gi += kAdamThreads) {
+      const uint4 wu = reinterpret_cast<const uint4*>(pw)[gi];
+      const uint4 gu = reinterpret_cast<const uint4*>(pg)[gi];
+      float4 m0 = reinterpret_cast<float4*>(pm)[gi * 2], m1 = reinterpret_cast<float4*>(pm)[gi * 2 + 1];
+      float4 v0 = reinterpret_cast<float4*>(pv)[gi * 2], v1 = reinterpret_cast<float4*>(pv)[gi * 2 + 1];
+      const uint32_t ww[4] = {wu.x, wu.y, wu.z, wu.w};
+      const uint32_t gg[4] = {gu.x, gu.y, gu.z, gu.w};
+      float w[8], g[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = unpack_bf16x2(ww[k]);
+        const float2 c = unpack_bf16x2(gg[k]);
+        w[2 * k] = a.x; w[2 * k + 1] = a.y;
+        g[2 * k] = c.x; g[2 * k + 1] = c.y;
+      }
+      float* mm[8] = {&m0.x, &m0.y, &m0.z, &m0.w, &m1.x, &m1.y, &m1.z, &m1.w};
+      float* vv[8] = {&v0.x, &v0.y, &v0.z, &v0.w, &v1.x, &v1.y, &v1.z, &v1.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) update(g[k], w[k], *mm[k], *vv[k]);
+      reinterpret_cast<float4*>(pm)[gi * 2] = m0;
+      reinterpret_cast<float4*>(pm)[gi * 2 + 1] = m1;
+      reinterpret_cast<float4*>(pv)[gi * 2] = v0;
+      reinterpret_cast<float4*>(pv)[gi * 2 + 1] = v1;
+      uint4 out;
+      out.x = pack_bf16x2(w[0], w[1]);
+      out.y = pack_bf16x2(w[2], w[3]);
+      out.z = pack_bf16x2(w[4], w[5]);
+      out.w = pack_bf16x2(w[6], w[7]);
+      reinterpret_cast<uint4*>(pw)[gi] = out;
+    }
+    done = groups * 8;
+  }
+  for (int i = done + threadIdx.x; i < count; i += kAdamThreads) {
     const long long idx = base + i;
-    if (idx >= t.numel) break;
     const float g = t.grad_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(t.grad)[idx])
                                 : static_cast<const float*>(t.grad)[idx];
     float w = t.param_bf16 ? __bfloat162float(static_cast<__nv_bfloat16*>(t.param)[idx])
                            : static_cast<float*>(t.param)[idx];
-    if (wd != 0.f) w *= decay;
-    const float m = t.exp_avg[idx] * b1 + g * (1.f - b1);
-    const float v = t.exp_avg_sq[idx] * b2 + g * g * (1.f - b2);
+    float m = t.exp_avg[idx], v = t.exp_avg_sq[idx];
+    update(g, w, m, v);
     t.exp_avg[idx] = m;
     t.exp_avg_sq[idx] = v;
-    const float denom = sqrtf(v) * inv_sqrt_corr2 + eps;
-    w -= step_size * (m / denom);
     if (t.param_bf16) static_cast<__nv_bfloat16*>(t.param)[idx] = __float2bfloat16(w);
     else static_cast<float*>(t.param)[idx] = w;
   }

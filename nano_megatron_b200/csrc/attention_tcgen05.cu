@@ -33,6 +33,23 @@ namespace nmb {
 constexpr int kMaxChunks = 8;
 constexpr int kAttnThreads = 192;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 of the growth tolerated before O is rescaled
+
+// Bulk (TMA) reduce-add of a contiguous fp32 span from shared to global memory.
+__device__ __forceinline__ void bulk_reduce_add_f32(float* gdst, const float* ssrc, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst),
+               "r"(smem_u32(ssrc)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct AttnFwdParams {
   CUtensorMap q_map;
@@ -213,40 +230,78 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       }
       tc_fence_after();
       const int kv0 = j * 128;
+      // A tile is "full" when every key of it is visible to every query row of
+      // this CTA: then no per-element masking is needed (CTA-uniform test).
+      const bool tile_full = (kv0 + 127 <= p.q_pos0 + q0) && (kv0 + 128 <= skv_total);
       int limit = q_pos - kv0;                       // columns <= limit are visible
       if (skv_total - 1 - kv0 < limit) limit = skv_total - 1 - kv0;
-      // pass 1: running maximum
-      float mx = m_run;
+      // pass 1: tile maximum
+      float mx = -INFINITY;
+      if (tile_full) {
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32];
-        tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
-        tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sr[32];
+          tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+          tmem_ld_wait();
+          float m0 = __uint_as_float(sr[0]), m1 = __uint_as_float(sr[1]);
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          const float s = (c * 32 + jj <= limit) ? __uint_as_float(sr[jj]) : -INFINITY;
-          mx = fmaxf(mx, s);
+          for (int jj = 2; jj < 32; jj += 2) {
+            m0 = fmaxf(m0, __uint_as_float(sr[jj]));
+            m1 = fmaxf(m1, __uint_as_float(sr[jj + 1]));
+          }
+          mx = fmaxf(mx, fmaxf(m0, m1));
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sr[32];
+          tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj)
+            if (c * 32 + jj <= limit) mx = fmaxf(mx, __uint_as_float(sr[jj]));
         }
       }
-      const float m_new = mx;
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f((m_run - m_use) * sl2);
+      // Lazy rescaling: the reference maximum only moves when the tile maximum
+      // exceeds it by more than 2^8 in the exponent domain, so most tiles need
+      // no pass over O; the final division by l makes the result exact.
+      float m_new = m_run;
+      if (mx > m_run + kRescaleThreshold / sl2) m_new = mx;
+      const float alpha = (m_new == m_run) ? 1.f : ((m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2));
+      const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new * sl2;
       // pass 2: probabilities
       uint32_t pk[64];
       float rowsum = 0.f;
+      if (tile_full) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32];
-        tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
-        tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sr[32];
+          tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+          tmem_ld_wait();
+          float r0 = 0.f, r1 = 0.f;
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) {
-          const float s0 = __uint_as_float(sr[jj]);
-          const float s1 = __uint_as_float(sr[jj + 1]);
-          const float p0 = (c * 32 + jj <= limit) ? exp2f((s0 - m_use) * sl2) : 0.f;
-          const float p1 = (c * 32 + jj + 1 <= limit) ? exp2f((s1 - m_use) * sl2) : 0.f;
-          rowsum += p0 + p1;
-          pk[c * 16 + jj / 2] = pack_bf16x2(p0, p1);
+          for (int jj = 0; jj < 32; jj += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[jj]), sl2, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[jj + 1]), sl2, neg_m));
+            r0 += p0;
+            r1 += p1;
+            pk[c * 16 + jj / 2] = pack_bf16x2(p0, p1);
+          }
+          rowsum += r0 + r1;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sr[32];
+          tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 2) {
+            const float p0 = (c * 32 + jj <= limit) ? fast_exp2(fmaf(__uint_as_float(sr[jj]), sl2, neg_m)) : 0.f;
+            const float p1 = (c * 32 + jj + 1 <= limit) ? fast_exp2(fmaf(__uint_as_float(sr[jj + 1]), sl2, neg_m)) : 0.f;
+            rowsum += p0 + p1;
+            pk[c * 16 + jj / 2] = pack_bf16x2(p0, p1);
+          }
         }
       }
       tc_fence_before();
@@ -353,7 +408,13 @@ struct AttnBwdSmem {
   static constexpr int kDO = kQ + kQStages * kTile;
   static constexpr int kP = kDO + kQStages * kTile;
   static constexpr int kDS = kP + 32768;
-  static constexpr int kBar = kDS + 32768;
+  // fp32 staging of the dQ tile for the bulk reduce-add.  HD == 64: its own
+  // buffer with rows padded by 16 B (no bank conflicts); HD == 128: aliases the
+  // P + dS buffers (64 KiB, unpadded rows).
+  static constexpr bool kStageAlias = HD > 64;
+  static constexpr int kStage = kStageAlias ? kP : kDS + 32768;
+  static constexpr int kStageBytes = kStageAlias ? 0 : 128 * (HD + 4) * 4;
+  static constexpr int kBar = kDS + 32768 + kStageBytes;
   static constexpr int kNumBars = 1 + 2 * kQStages + 4;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
@@ -518,15 +579,23 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       const bool valid = q_row < p.Sq;
       const long long stat_idx = (static_cast<long long>(b) * p.Hq + hq) * p.Sq + q_row;
       const float lse2 = valid ? p.lse[stat_idx] * kLog2e : 0.f;
-      const float dlt = valid ? p.delta[stat_idx] : 0.f;
+      const float dlt_s = valid ? p.delta[stat_idx] * p.scale : 0.f;
       int limit = p.q_pos0 + q_row - kv0;
       if (skv_total - 1 - kv0 < limit) limit = skv_total - 1 - kv0;
       if (!valid) limit = -1;
+      // CTA-uniform: every (query, key) pair of this tile is visible and valid.
+      const bool tile_full = (kv0 + 127 <= p.q_pos0 + q0) && (q0 + 127 < p.Sq) && (kv0 + 128 <= skv_total);
       if (!mbar_wait(sdp_full, i & 1, abort_flag, p.status, 48)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      if (L::kStageAlias && i > 0) {
+        // The dQ staging rows alias P / dS: every thread's bulk reduce must have
+        // finished reading before anyone overwrites them.
+        bulk_wait_read();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
       uint8_t* sp = smem + L::kP;
       uint8_t* sds = smem + L::kDS;
 #pragma unroll 1
@@ -536,16 +605,28 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         tmem_ld_32x32(t_lane + kDPCol + c * 32, dpr);
         tmem_ld_wait();
         uint32_t pp[16], dd[16];
+        if (tile_full) {
 #pragma unroll
-        for (int jj = 0; jj < 32; jj += 2) {
-          const bool v0 = c * 32 + jj <= limit;
-          const bool v1 = c * 32 + jj + 1 <= limit;
-          const float p0 = v0 ? exp2f(__uint_as_float(sr[jj]) * sl2 - lse2) : 0.f;
-          const float p1 = v1 ? exp2f(__uint_as_float(sr[jj + 1]) * sl2 - lse2) : 0.f;
-          const float d0 = p0 * (__uint_as_float(dpr[jj]) - dlt) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dpr[jj + 1]) - dlt) * p.scale;
-          pp[jj / 2] = pack_bf16x2(p0, p1);
-          dd[jj / 2] = pack_bf16x2(d0, d1);
+          for (int jj = 0; jj < 32; jj += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[jj]), sl2, -lse2));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[jj + 1]), sl2, -lse2));
+            const float d0 = p0 * fmaf(__uint_as_float(dpr[jj]), p.scale, -dlt_s);
+            const float d1 = p1 * fmaf(__uint_as_float(dpr[jj + 1]), p.scale, -dlt_s);
+            pp[jj / 2] = pack_bf16x2(p0, p1);
+            dd[jj / 2] = pack_bf16x2(d0, d1);
+          }
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 32; jj += 2) {
+            const bool v0 = c * 32 + jj <= limit;
+            const bool v1 = c * 32 + jj + 1 <= limit;
+            const float p0 = v0 ? fast_exp2(fmaf(__uint_as_float(sr[jj]), sl2, -lse2)) : 0.f;
+            const float p1 = v1 ? fast_exp2(fmaf(__uint_as_float(sr[jj + 1]), sl2, -lse2)) : 0.f;
+            const float d0 = p0 * fmaf(__uint_as_float(dpr[jj]), p.scale, -dlt_s);
+            const float d1 = p1 * fmaf(__uint_as_float(dpr[jj + 1]), p.scale, -dlt_s);
+            pp[jj / 2] = pack_bf16x2(p0, p1);
+            dd[jj / 2] = pack_bf16x2(d0, d1);
+          }
         }
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -562,20 +643,33 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         break;
       }
       tc_fence_after();
-      float* dq_row = p.dq_acc + ((static_cast<long long>(b) * p.Sq + q_row) * p.Hq + hq) * p.d;
+      // dQ tile: TMEM -> fp32 staging row of this thread -> one bulk reduce-add
+      // per row into the global accumulator (replaces 64..128 scalar atomics).
+      const int pitch = L::kStageAlias ? p.d : HD + 4;  // floats
+      float* stage_row = reinterpret_cast<float*>(smem + L::kStage) + r * pitch;
+      if (!L::kStageAlias) bulk_wait_read();  // my previous reduce has read its row
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t qr[32];
         tmem_ld_32x32(t_lane + kDQCol + c * 32, qr);
         tmem_ld_wait();
-        if (valid && c * 32 < p.d) {
+        if (c * 32 < p.d) {
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) atomicAdd(dq_row + c * 32 + jj, __uint_as_float(qr[jj]));
+          for (int q4 = 0; q4 < 8; ++q4)
+            *reinterpret_cast<uint4*>(stage_row + c * 32 + q4 * 4) =
+                make_uint4(qr[q4 * 4], qr[q4 * 4 + 1], qr[q4 * 4 + 2], qr[q4 * 4 + 3]);
         }
       }
       tc_fence_before();
       mbar_arrive(dq_empty);
+      fence_proxy_async_smem();
+      if (valid) {
+        float* dq_row = p.dq_acc + ((static_cast<long long>(b) * p.Sq + q_row) * p.Hq + hq) * p.d;
+        bulk_reduce_add_f32(dq_row, stage_row, p.d * 4);
+      }
+      bulk_commit();
     }
+    bulk_wait_all();
     // dK / dV of this tile: the last dq_full also covers their MMAs.
     const int kv_row = kv_row0 + r;
     if (ok && kv_row < p.chunk_len) {
