@@ -792,12 +792,28 @@ struct NmbTensor4 {
   long long stride_b, stride_s, stride_h;
 };
 
+// Opt the attention kernels in to their dynamic shared memory sizes (once per
+// process and device, right after the library is loaded).
+extern "C" int nmb_attn_configure() {
+  cudaError_t e;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnFwdSmem<64>::kTotal);
+  if (e != cudaSuccess) return 300 + e;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnFwdSmem<128>::kTotal);
+  if (e != cudaSuccess) return 300 + e;
+  e = cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem<64>::kTotal);
+  if (e != cudaSuccess) return 300 + e;
+  e = cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem<128>::kTotal);
+  if (e != cudaSuccess) return 300 + e;
+  return 0;
+}
+
 extern "C" int nmb_attn_fwd(const NmbTensor4* q, const NmbTensor4* k_chunks, const NmbTensor4* v_chunks,
                             int n_chunks, int chunk_len, const NmbTensor4* o, float* lse, int B, int Hq,
                             int Hkv, int Sq, int d, int q_pos0, float scale, int* status, void* stream) {
   if (n_chunks < 1 || n_chunks > kMaxChunks) return kBadArgument;
   if (d != 64 && d != 96 && d != 128) return kBadArgument;
   if (n_chunks > 1 && (chunk_len % 128) != 0) return kBadArgument;
+  (void)cudaGetLastError();
   AttnFwdParams p;
   if (make_attn_map(&p.q_map, q->ptr, d, Sq, Hq, B, q->stride_s, q->stride_h, q->stride_b)) return 101;
   for (int c = 0; c < n_chunks; ++c) {
@@ -820,20 +836,8 @@ extern "C" int nmb_attn_fwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (d == 64) {
-    static bool cfg = false;
-    if (!cfg) {
-      e = cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnFwdSmem<64>::kTotal);
-      if (e != cudaSuccess) return 300 + e;
-      cfg = true;
-    }
     attn_fwd_kernel<64><<<grid, kAttnThreads, AttnFwdSmem<64>::kTotal, s>>>(p);
   } else {
-    static bool cfg = false;
-    if (!cfg) {
-      e = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnFwdSmem<128>::kTotal);
-      if (e != cudaSuccess) return 300 + e;
-      cfg = true;
-    }
     attn_fwd_kernel<128><<<grid, kAttnThreads, AttnFwdSmem<128>::kTotal, s>>>(p);
   }
   e = cudaGetLastError();
@@ -851,6 +855,7 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   if (d != 64 && d != 96 && d != 128) return kBadArgument;
   if (n_chunks > 1 && (chunk_len % 128) != 0) return kBadArgument;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  (void)cudaGetLastError();
   {
     const long long rows = static_cast<long long>(B) * Sq * Hq;
     const int threads = 256;
@@ -882,20 +887,8 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   dim3 grid(n_visible_kv_tiles, Hkv, B);
   cudaError_t e;
   if (d == 64) {
-    static bool cfg = false;
-    if (!cfg) {
-      e = cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem<64>::kTotal);
-      if (e != cudaSuccess) return 300 + e;
-      cfg = true;
-    }
     attn_bwd_kernel<64><<<grid, kAttnThreads, AttnBwdSmem<64>::kTotal, s>>>(p);
   } else {
-    static bool cfg = false;
-    if (!cfg) {
-      e = cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem<128>::kTotal);
-      if (e != cudaSuccess) return 300 + e;
-      cfg = true;
-    }
     attn_bwd_kernel<128><<<grid, kAttnThreads, AttnBwdSmem<128>::kTotal, s>>>(p);
   }
   e = cudaGetLastError();

@@ -1,0 +1,342 @@
+// Peer-memory collectives over NVLink / NVSwitch: kernels that read and write
+// other GPUs' buffers directly (symmetric allocations exchanged through CUDA
+// IPC) and synchronise through flags in a symmetric "signal pad".
+//
+// They replace NCCL calls of the reference where a collective is fused with
+// arithmetic: the bucketed gradient all-reduce + divide of its DDP
+// (nano_megatron/distributed/bucket.py:85-100) becomes one kernel that reads the
+// peers' buckets, sums in fp32, scales by 1/(dp*cp) and writes the result.
+//
+// Synchronisation.  A signal pad is `kChannels x kMaxBlocks x kMaxRanks` 32-bit
+// flags per rank.  Block b of a kernel on channel c signals by storing its
+// epoch into slot [c][b][my_rank] of every peer's pad and waits until its own
+// pad's slots [c][b][*] have reached that epoch.  The epoch of (c, b) lives in
+// device memory owned by that block, so a replayed CUDA graph keeps counting.
+// All ranks of a group must launch the same kernels on a channel in the same
+// order.  Every wait is bounded; a timed-out wait stores kPeerTimeout in the
+// status word and the block stops touching peer memory.
+//
+// Only plain peer loads / stores are used (no multimem, no TMA multicast).
+#include "common.cuh"
+
+#include <string.h>
+
+namespace nmb {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxBlocks = 256;
+constexpr int kChannels = 4;
+
+struct PeerPtrs {
+  void* p[kMaxRanks];
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint32_t* pad_slot(void* pad, int channel, int block, int rank) {
+  return static_cast<uint32_t*>(pad) + (static_cast<size_t>(channel) * kMaxBlocks + block) * kMaxRanks + rank;
+}
+
+// Block-level barrier with the same block index on every rank of the group.
+// `budget` in clock cycles.  Returns false (for the whole block) on a timeout.
+__device__ bool block_barrier(const PeerPtrs& pads, int channel, int rank, int n, uint32_t epoch, int* status,
+                              long long budget, int where) {
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();  // the block's earlier writes are ordered before the signal
+  if (threadIdx.x < n) {
+    __threadfence_system();
+    st_release_sys(pad_slot(pads.p[threadIdx.x], channel, blockIdx.x, rank), epoch);
+    const uint32_t* mine = pad_slot(pads.p[rank], channel, blockIdx.x, threadIdx.x);
+    const long long t0 = clock64();
+    // epochs only grow; compare as signed distance so wrap-around is harmless
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
+      if (clock64() - t0 > budget) {
+        report_status(status, kPeerTimeout, where);
+        failed = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const bool ok = failed == 0;
+  __syncthreads();  // `failed` is reused by the next barrier of this block
+  return ok;
+}
+
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  static __device__ __forceinline__ void add(float* acc, const uint4& u) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack_bf16x2(w[k]);
+      acc[2 * k] += f.x;
+      acc[2 * k + 1] += f.y;
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float* acc, float scale) {
+    uint4 o;
+    o.x = pack_bf16x2(acc[0] * scale, acc[1] * scale);
+    o.y = pack_bf16x2(acc[2] * scale, acc[3] * scale);
+    o.z = pack_bf16x2(acc[4] * scale, acc[5] * scale);
+    o.w = pack_bf16x2(acc[6] * scale, acc[7] * scale);
+    return o;
+  }
+};
+template <>
+struct Vec16<float> {
+  static constexpr int kElems = 4;
+  static __device__ __forceinline__ void add(float* acc, const uint4& u) {
+    acc[0] += __uint_as_float(u.x);
+    acc[1] += __uint_as_float(u.y);
+    acc[2] += __uint_as_float(u.z);
+    acc[3] += __uint_as_float(u.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float* acc, float scale) {
+    return make_uint4(__float_as_uint(acc[0] * scale), __float_as_uint(acc[1] * scale),
+                      __float_as_uint(acc[2] * scale), __float_as_uint(acc[3] * scale));
+  }
+};
+
+// In-place all-reduce (sum) * scale of a symmetric buffer, two-shot:
+//   block b owns the b-th slice of the buffer on every rank; inside it rank r
+//   reduces the r-th sub-slice (reading all peers), then every rank copies the
+//   other ranks' reduced sub-slices.  Dependencies therefore stay between
+//   blocks of equal index, which is what `block_barrier` synchronises.
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_scale_kernel(PeerPtrs bufs, PeerPtrs pads, uint32_t* epochs, int channel, int rank, int n,
+                       long long n_vec, float scale, int* status, long long budget) {
+  using V = Vec16<T>;
+  __shared__ uint32_t epoch_s;
+  uint32_t* my_epoch = epochs + channel * kMaxBlocks + blockIdx.x;
+  if (threadIdx.x == 0) epoch_s = *my_epoch;
+  __syncthreads();
+  const uint32_t e0 = epoch_s;
+  const long long per_block = (n_vec + gridDim.x - 1) / gridDim.x;
+  const long long blk_lo = per_block * blockIdx.x;
+  long long blk_hi = blk_lo + per_block;
+  if (blk_hi > n_vec) blk_hi = n_vec;
+  const long long blk_len = blk_hi > blk_lo ? blk_hi - blk_lo : 0;
+  const long long per_rank = (blk_len + n - 1) / n;
+
+  constexpr int U = 8;  // independent 16-byte loads in flight per thread (NVLink latency is ~2 us)
+  bool ok = block_barrier(pads, channel, rank, n, e0 + 1, status, budget, 61);  // peers' inputs are ready
+  if (ok) {
+    const long long lo = blk_lo + per_rank * rank;
+    long long hi = lo + per_rank;
+    if (hi > blk_hi) hi = blk_hi;
+    uint4* mine = static_cast<uint4*>(bufs.p[rank]);
+    for (long long base = lo + threadIdx.x; base < hi; base += static_cast<long long>(blockDim.x) * U) {
+      float acc[U][V::kElems];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int k = 0; k < V::kElems; ++k) acc[u][k] = 0.f;
+#pragma unroll 1
+      for (int k = 0; k < n; ++k) {
+        const uint4* src = static_cast<const uint4*>(bufs.p[(rank + k) % n]);  // start at home, spread the peers
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = base + static_cast<long long>(u) * blockDim.x;
+          v[u] = i < hi ? src[i] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) V::add(acc[u], v[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + static_cast<long long>(u) * blockDim.x;
+        if (i < hi) mine[i] = V::pack(acc[u], scale);
+      }
+    }
+  }
+  ok = ok && block_barrier(pads, channel, rank, n, e0 + 2, status, budget, 62);  // all sub-slices reduced
+  if (ok) {
+    uint4* mine = static_cast<uint4*>(bufs.p[rank]);
+    for (int k = 1; k < n; ++k) {
+      const int src = (rank + k) % n;
+      const long long lo = blk_lo + per_rank * src;
+      long long hi = lo + per_rank;
+      if (hi > blk_hi) hi = blk_hi;
+      const uint4* theirs = static_cast<const uint4*>(bufs.p[src]);
+      for (long long base = lo + threadIdx.x; base < hi; base += static_cast<long long>(blockDim.x) * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = base + static_cast<long long>(u) * blockDim.x;
+          if (i < hi) v[u] = theirs[i];
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = base + static_cast<long long>(u) * blockDim.x;
+          if (i < hi) mine[i] = v[u];
+        }
+      }
+    }
+  }
+  // nobody may overwrite a buffer a peer is still copying from
+  block_barrier(pads, channel, rank, n, e0 + 3, status, budget, 63);
+  if (threadIdx.x == 0) *my_epoch = e0 + 3;
+}
+
+// Stand-alone barrier (one block), e.g. "my buffer is published" between kernels.
+__global__ void barrier_kernel(PeerPtrs pads, uint32_t* epochs, int channel, int rank, int n, int* status,
+                               long long budget) {
+  __shared__ uint32_t epoch_s;
+  uint32_t* my_epoch = epochs + channel * kMaxBlocks + blockIdx.x;
+  if (threadIdx.x == 0) epoch_s = *my_epoch;
+  __syncthreads();
+  block_barrier(pads, channel, rank, n, epoch_s + 1, status, budget, 64);
+  if (threadIdx.x == 0) *my_epoch = epoch_s + 1;
+}
+
+// Waits for a flag that nobody sets unless `release` is non-zero: used by the
+// tests of the bounded-wait path (the wait must end with kPeerTimeout and the
+// context must stay usable).
+__global__ void bounded_wait_probe_kernel(const uint32_t* flag, uint32_t want, int* status, long long budget) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - want) < 0) {
+    if (clock64() - t0 > budget) {
+      report_status(status, kPeerTimeout, 65);
+      return;
+    }
+  }
+}
+
+// out[rows, cols] = sum over `n` slots of partial[slot][rows, cols] (+ bias[cols]) (+ residual[rows, cols]).
+// Second half of the GEMM -> reduce-scatter path: every peer has stored its
+// partial tile for this rank's rows into slot [peer] of this rank's staging.
+__global__ void slot_sum_kernel(const __nv_bfloat16* __restrict__ partial, int n, long long slot_elems,
+                                const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
+                                __nv_bfloat16* __restrict__ out, long long rows, int cols) {
+  const long long vecs = slot_elems / 8;
+  const int cvec = cols / 8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int s = 0; s < n; ++s)
+      Vec16<__nv_bfloat16>::add(acc, reinterpret_cast<const uint4*>(partial + s * slot_elems)[i]);
+    if (bias != nullptr) Vec16<__nv_bfloat16>::add(acc, reinterpret_cast<const uint4*>(bias)[i % cvec]);
+    if (residual != nullptr) Vec16<__nv_bfloat16>::add(acc, reinterpret_cast<const uint4*>(residual)[i]);
+    reinterpret_cast<uint4*>(out)[i] = Vec16<__nv_bfloat16>::pack(acc, 1.f);
+  }
+}
+
+}  // namespace nmb
+
+using namespace nmb;
+
+// ---------------------------------------------------------------- allocation --
+extern "C" int nmb_symm_alloc(long long bytes, void** ptr, unsigned char* handle64) {
+  cudaError_t e = cudaMalloc(ptr, static_cast<size_t>(bytes));
+  if (e != cudaSuccess) return 400 + e;
+  e = cudaMemset(*ptr, 0, static_cast<size_t>(bytes));
+  if (e != cudaSuccess) return 400 + e;
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, *ptr);
+  if (e != cudaSuccess) return 400 + e;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+
+extern "C" int nmb_symm_open(const unsigned char* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+extern "C" int nmb_symm_close(void* ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+extern "C" int nmb_symm_free(void* ptr) {
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+extern "C" int nmb_comm_limits(int* max_ranks, int* max_blocks, int* channels) {
+  *max_ranks = kMaxRanks;
+  *max_blocks = kMaxBlocks;
+  *channels = kChannels;
+  return 0;
+}
+
+static void fill(PeerPtrs& t, void* const* src, int n) {
+  for (int i = 0; i < kMaxRanks; ++i) t.p[i] = i < n ? src[i] : nullptr;
+}
+
+// bufs[n], pads[n]: per-rank device pointers (peer-mapped); numel elements of
+// bf16 (is_bf16) or fp32.  numel * elem_size must be a multiple of 16.
+extern "C" int nmb_allreduce_scale(void* const* bufs, void* const* pads, void* epochs, int channel, int rank,
+                                   int n, long long numel, int is_bf16, float scale, int blocks, int* status,
+                                   long long budget_cycles, void* stream) {
+  if (n < 1 || n > kMaxRanks || channel < 0 || channel >= kChannels) return kBadArgument;
+  const int per = is_bf16 ? 8 : 4;
+  if (numel % per != 0) return kBadArgument;
+  if (blocks < 1) blocks = 1;
+  if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  PeerPtrs b, p;
+  fill(b, bufs, n);
+  fill(p, pads, n);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (is_bf16)
+    allreduce_scale_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
+                                                                numel / per, scale, status, budget_cycles);
+  else
+    allreduce_scale_kernel<float><<<blocks, 512, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
+                                                         numel / per, scale, status, budget_cycles);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+extern "C" int nmb_symm_barrier(void* const* pads, void* epochs, int channel, int rank, int n, int* status,
+                                long long budget_cycles, void* stream) {
+  if (n < 1 || n > kMaxRanks || channel < 0 || channel >= kChannels) return kBadArgument;
+  PeerPtrs p;
+  fill(p, pads, n);
+  barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, static_cast<uint32_t*>(epochs), channel, rank, n,
+                                                                  status, budget_cycles);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+extern "C" int nmb_bounded_wait_probe(const void* flag, unsigned want, int* status, long long budget_cycles,
+                                      void* stream) {
+  bounded_wait_probe_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(flag), want,
+                                                                            status, budget_cycles);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+extern "C" int nmb_slot_sum(const void* partial, int n, long long slot_elems, const void* bias, const void* residual,
+                            void* out, long long rows, int cols, void* stream) {
+  if (slot_elems % 8 != 0 || cols % 8 != 0) return kBadArgument;
+  const long long vecs = slot_elems / 8;
+  int blocks = static_cast<int>((vecs + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  slot_sum_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(partial), n, slot_elems, static_cast<const __nv_bfloat16*>(bias),
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), rows, cols);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}

@@ -263,6 +263,15 @@ inline int make_tmap_bf16(CUtensorMap* map, const void* ptr, int rank, const uin
                           const uint64_t* strides_bytes, const uint32_t* box) {
   EncodeTiledFn fn = get_encode_tiled();
   if (fn == nullptr) return -1;
+  // The encoder is a driver-API call and needs a context bound to the calling
+  // host thread; a fresh thread (e.g. an autograd worker whose first CUDA call
+  // is one of our launchers) has none until a runtime call binds the primary
+  // context of its current device.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   cuuint64_t d[5];
   cuuint64_t s[4];
   cuuint32_t b[5];

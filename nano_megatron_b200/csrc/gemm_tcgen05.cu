@@ -392,12 +392,6 @@ static int launch_gemm(const void* A, int lda, const void* B, int ldb, const Gem
 
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
   const int smem_bytes = L::kTotal + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) return 300 + static_cast<int>(e);
-    configured = true;
-  }
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, kGemmThreads, smem_bytes, stream>>>(ta, tb, ep, M, N, K, status);
@@ -416,7 +410,31 @@ static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const G
   return launch_gemm<128, 6, A_MN, B_MN>(A, lda, B, ldb, ep, M, N, K, status, stream);
 }
 
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int configure_gemm() {
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN, STAGES>::kTotal + 1024);
+  return e == cudaSuccess ? 0 : 300 + static_cast<int>(e);
+}
+
 }  // namespace nmb
+
+// Opt every GEMM variant in to its dynamic shared memory size on the current
+// device.  Called once per process (per device) right after the library is
+// loaded, from the thread that loads it.
+extern "C" int nmb_gemm_configure() {
+  using namespace nmb;
+  int rc = 0;
+  rc |= configure_gemm<256, 4, false, false>();
+  rc |= configure_gemm<256, 4, false, true>();
+  rc |= configure_gemm<256, 4, true, true>();
+  rc |= configure_gemm<256, 4, true, false>();
+  rc |= configure_gemm<128, 6, false, false>();
+  rc |= configure_gemm<128, 6, false, true>();
+  rc |= configure_gemm<128, 6, true, true>();
+  rc |= configure_gemm<128, 6, true, false>();
+  return rc;
+}
 
 // C[M,N] = epilogue(alpha * A B^T).  `a_mn` / `b_mn` say that the operand is
 // stored with its M/N index contiguous (i.e. as [K, M] / [K, N]).  Leading
@@ -430,6 +448,7 @@ extern "C" int nmb_gemm_bf16(const void* A, int lda, int a_mn, const void* B, in
                              int* status, void* stream) {
   using namespace nmb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  (void)cudaGetLastError();  // a stale error of this host thread is not ours to report
   if ((lda % 8) != 0 || (ldb % 8) != 0) return kBadArgument;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return kBadArgument;
   GemmEpilogue ep;

@@ -1,0 +1,178 @@
+"""Symmetric memory over CUDA IPC: buffers that every rank of a process group
+can address directly, plus the signal pads the peer-memory kernels use.
+
+A :class:`SymmetricWorkspace` belongs to one process group of GPUs on one node.
+``alloc_tensor`` is a collective over that group: every rank allocates the same
+number of bytes, the IPC handles are exchanged with ``all_gather_object`` and
+each rank maps its peers' allocations, so a kernel can be handed the table of
+all ranks' pointers (``csrc/comm.cu``).  Plain peer loads and stores only --
+no multicast objects are created.
+
+The reference has no counterpart: its only transport is ``torch.distributed``
+(nano_megatron/distributed/torch_backend.py:22-80).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from . import symmetric
+
+#: ~1 s at 1.9 GHz; a peer that never arrives ends the wait with a status code
+DEFAULT_BUDGET_CYCLES = 2_000_000_000
+CHANNEL_TP, CHANNEL_DP, CHANNEL_CP, CHANNEL_AUX = 0, 1, 2, 3
+
+
+class _RawCuda:
+    """Exposes a raw device pointer through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class SymmetricAllocation:
+    def __init__(self, local_ptr: int, peer_ptrs: list[int], nbytes: int, device: torch.device) -> None:
+        self.local_ptr, self.peer_ptrs, self.nbytes = local_ptr, peer_ptrs, nbytes
+        self.bytes = torch.as_tensor(_RawCuda(local_ptr, nbytes), device=device)
+
+    def table(self):
+        arr = (ctypes.c_void_p * len(self.peer_ptrs))()
+        for i, p in enumerate(self.peer_ptrs):
+            arr[i] = p
+        return arr
+
+
+class SymmetricWorkspace:
+    def __init__(self, group: Any, *, budget_cycles: int = DEFAULT_BUDGET_CYCLES) -> None:
+        self.group = group
+        self.size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.budget = int(budget_cycles)
+        lib = native.lib()
+        mr, mb, ch = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        lib.nmb_comm_limits(ctypes.byref(mr), ctypes.byref(mb), ctypes.byref(ch))
+        self.max_ranks, self.max_blocks, self.channels = mr.value, mb.value, ch.value
+        if self.size > self.max_ranks:
+            raise RuntimeError(f"group of {self.size} ranks exceeds the kernel limit of {self.max_ranks}")
+        self._allocs: list[SymmetricAllocation] = []
+        self._by_ptr: dict[int, tuple[SymmetricAllocation, int]] = {}
+        self.pad = self._alloc_raw(self.channels * self.max_blocks * self.max_ranks * 4)
+        self.epochs = torch.zeros(self.channels * self.max_blocks, dtype=torch.int32, device=self.device)
+        self.status = native.status_word(self.device)
+        dist.barrier(group=group)
+
+    # ------------------------------------------------------------ allocation --
+    def _alloc_raw(self, nbytes: int) -> SymmetricAllocation:
+        nbytes = (int(nbytes) + 255) // 256 * 256
+        lib = native.lib()
+        ptr = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        native.check_rc(lib.nmb_symm_alloc(ctypes.c_longlong(nbytes), ctypes.byref(ptr), handle), "nmb_symm_alloc")
+        native.launches -= 1  # not a kernel
+        mine = bytes(handle)
+        everyone: list[Any] = [None] * self.size
+        dist.all_gather_object(everyone, (mine, nbytes), group=self.group)
+        peers: list[int] = []
+        for r, (h, nb) in enumerate(everyone):
+            if nb != nbytes:
+                raise RuntimeError("symmetric allocation sizes differ between ranks")
+            if r == self.rank:
+                peers.append(ptr.value)
+                continue
+            remote = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+            native.check_rc(lib.nmb_symm_open(buf, ctypes.byref(remote)), "nmb_symm_open")
+            native.launches -= 1
+            peers.append(remote.value)
+        alloc = SymmetricAllocation(ptr.value, peers, nbytes, self.device)
+        self._allocs.append(alloc)
+        return alloc
+
+    def alloc_tensor(self, numel: int, dtype: torch.dtype) -> Optional[torch.Tensor]:
+        """Collective: a zero-filled 1-D tensor of ``numel`` elements in symmetric memory."""
+        item = torch.empty((), dtype=dtype).element_size()
+        alloc = self._alloc_raw(numel * item)
+        t = alloc.bytes[: numel * item].view(dtype)
+        self._by_ptr[t.data_ptr()] = (alloc, 0)
+        return t
+
+    def peers_of(self, t: torch.Tensor) -> list[int]:
+        """Device pointers of ``t``'s counterpart on every rank (``t`` must come from ``alloc_tensor``)."""
+        for alloc in self._allocs:
+            off = t.data_ptr() - alloc.local_ptr
+            if 0 <= off < alloc.nbytes:
+                return [p + off for p in alloc.peer_ptrs]
+        raise ValueError("tensor is not in symmetric memory of this workspace")
+
+    def peer_table(self, t: torch.Tensor):
+        ptrs = self.peers_of(t)
+        arr = (ctypes.c_void_p * len(ptrs))()
+        for i, p in enumerate(ptrs):
+            arr[i] = p
+        return arr
+
+    def peer_view(self, t: torch.Tensor, rank: int) -> torch.Tensor:
+        """``t``'s counterpart on ``rank`` as a tensor of this process (peer-mapped memory)."""
+        if rank == self.rank:
+            return t
+        ptr = self.peers_of(t)[rank]
+        nbytes = t.numel() * t.element_size()
+        raw = torch.as_tensor(_RawCuda(ptr, nbytes), device=self.device)
+        return raw.view(t.dtype).view(t.shape)
+
+    # ------------------------------------------------------------ collectives --
+    def barrier(self, channel: int = CHANNEL_AUX) -> None:
+        """Device-side barrier of the group on the current stream (one tiny kernel)."""
+        rc = native.lib().nmb_symm_barrier(self.pad.table(), native.ptr(self.epochs), ctypes.c_int(channel),
+                                           ctypes.c_int(self.rank), ctypes.c_int(self.size), native.ptr(self.status),
+                                           ctypes.c_longlong(self.budget), native.stream_ptr(self.device))
+        native.check_rc(rc, "nmb_symm_barrier")
+
+    def all_reduce_scale_(self, t: torch.Tensor, scale: float, *, channel: int = CHANNEL_DP, blocks: int = 128) -> None:
+        """In-place ``t = sum_over_ranks(t) * scale`` for a tensor from ``alloc_tensor``."""
+        assert t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous()
+        rc = native.lib().nmb_allreduce_scale(
+            self.peer_table(t), self.pad.table(), native.ptr(self.epochs), ctypes.c_int(channel),
+            ctypes.c_int(self.rank), ctypes.c_int(self.size), ctypes.c_longlong(t.numel()),
+            ctypes.c_int(int(t.dtype == torch.bfloat16)), ctypes.c_float(scale), ctypes.c_int(blocks),
+            native.ptr(self.status), ctypes.c_longlong(self.budget), native.stream_ptr(self.device))
+        native.check_rc(rc, "nmb_allreduce_scale")
+
+    def make_allreduce_mean(self, flat: torch.Tensor) -> Callable[[torch.Tensor, int], bool]:
+        """Reducer for a DDP bucket whose buffer is ``flat`` (see ``GradBucket.fused_reduce``)."""
+        per = 8 if flat.dtype == torch.bfloat16 else 4
+        table, pads = self.peer_table(flat), self.pad.table()
+
+        def reduce(buf: torch.Tensor, divisor: int) -> bool:
+            if buf.data_ptr() != flat.data_ptr() or buf.numel() % per != 0:
+                return False
+            rc = native.lib().nmb_allreduce_scale(
+                table, pads, native.ptr(self.epochs), ctypes.c_int(CHANNEL_DP), ctypes.c_int(self.rank),
+                ctypes.c_int(self.size), ctypes.c_longlong(buf.numel()), ctypes.c_int(int(buf.dtype == torch.bfloat16)),
+                ctypes.c_float(1.0 / divisor), ctypes.c_int(128), native.ptr(self.status),
+                ctypes.c_longlong(self.budget), native.stream_ptr(self.device))
+            native.check_rc(rc, "nmb_allreduce_scale")
+            return True
+
+        return reduce
+
+
+def enable_symmetric_memory(ctx: Any) -> dict[str, SymmetricWorkspace]:
+    """Create and register workspaces for the TP, CP and DP x CP groups of ``ctx``
+    (those with more than one rank).  Collective over the whole job."""
+    made: dict[str, SymmetricWorkspace] = {}
+    for name, group, size in (
+        ("tp", ctx.tensor_parallel_group, ctx.tensor_parallel_size),
+        ("cp", ctx.context_parallel_group, ctx.context_parallel_size),
+        ("dp-cp", ctx.data_context_parallel_group, ctx.data_parallel_size * ctx.context_parallel_size),
+    ):
+        if size > 1 and symmetric.workspace_for(group) is None:
+            ws = SymmetricWorkspace(group)
+            symmetric.register_workspace(group, ws)
+            made[name] = ws
+    return made

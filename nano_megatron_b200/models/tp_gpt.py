@@ -359,6 +359,12 @@ class TPGPT(nn.Module):
                              "when sequence_parallel is enabled")
         if self._cp_size > 1 and seq_len % self._cp_size != 0:
             raise ValueError(f"seq_len ({seq_len}) must be divisible by context_parallel_size ({self._cp_size})")
+        if self._cp_size > 1:
+            from ..distributed import symmetric
+            ws = symmetric.workspace_for(self._cp_group)
+            if ws is not None:
+                from ..distributed.symm_ops import begin_step
+                begin_step(ws)
         x, local_positions = self.embed(input_ids, positions)
         # Under SP attention still sees the full sequence, so the blocks get
         # the full positions; under CP they get the local slice.

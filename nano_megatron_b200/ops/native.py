@@ -34,6 +34,24 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
+_configured_devices: set[int] = set()
+
+
+def _configure_current_device(loaded: ctypes.CDLL) -> None:
+    """Shared-memory opt-ins of the big kernels are per device: set them the
+    first time the library is used with a given device current."""
+    if not torch.cuda.is_available():
+        return
+    dev = torch.cuda.current_device()
+    if dev in _configured_devices:
+        return
+    for fn in (loaded.nmb_gemm_configure, loaded.nmb_attn_configure):
+        rc = fn()
+        if rc != 0:
+            raise NativeKernelError(f"kernel configuration failed with code {rc} on device {dev}")
+    _configured_devices.add(dev)
+
+
 def lib() -> ctypes.CDLL:
     """Load (once) and return the kernel library."""
     global _lib
@@ -46,6 +64,7 @@ def lib() -> ctypes.CDLL:
                         "(the CUDA ops do not fall back to PyTorch on a GPU)"
                     )
                 _lib = ctypes.CDLL(str(_LIB_PATH))
+    _configure_current_device(_lib)
     return _lib
 
 

@@ -30,6 +30,9 @@ def launch(script: str, worker: str, world: int, *, timeout: int = 300, extra_en
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr=127.0.0.1", f"--master-port={port_for(script + worker + str(world))}", script]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    for line in proc.stdout.splitlines():
+        if line.startswith("PERF"):
+            print(line)
     if proc.returncode != 0:
         tail = (proc.stdout[-3000:] + "\n" + proc.stderr[-6000:])
         raise AssertionError(f"distributed worker {worker} (world {world}) failed:\n{tail}")

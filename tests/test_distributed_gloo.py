@@ -379,4 +379,5 @@ def test_gloo(worker, world):
     launch(HERE, worker, world, timeout=180)
 
 
-run_worker_if_requested(globals())
+if __name__ == "__main__":
+    run_worker_if_requested(globals())
