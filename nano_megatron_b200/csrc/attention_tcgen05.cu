@@ -726,49 +726,67 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
 }
 
 // delta[b,h,s] = sum_d dO * O ; also clears the fp32 dQ accumulator.
+// d / 8 threads per (b, s, h) row, 16 bytes of O and dO per thread.
 __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dO,
                                      long long o_sb, long long o_ss, long long o_sh, long long do_sb,
                                      long long do_ss, long long do_sh, float* __restrict__ delta,
                                      float* __restrict__ dq_acc, int B, int H, int S, int d) {
-  // one warp per (b, s, h) row
-  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  const int per_row = d >> 3;                       // 8, 12 or 16 threads per row
+  const int group = per_row <= 8 ? 8 : 16;          // shuffle width (power of two)
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = gid / group;
+  const int part = gid % group;
   const long long total = static_cast<long long>(B) * S * H;
-  if (row >= total) return;
-  const int h = row % H;
-  const long long bs = row / H;
-  const int s = bs % S;
-  const int b = bs / S;
-  const __nv_bfloat16* orow = o + b * o_sb + s * o_ss + h * o_sh;
-  const __nv_bfloat16* drow = dO + b * do_sb + s * do_ss + h * do_sh;
   float acc = 0.f;
-  for (int c = lane * 2; c < d; c += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(orow + c));
-    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(drow + c));
-    acc += a.x * g.x + a.y * g.y;
-  }
+  if (row < total && part < per_row) {
+    const int h = row % H;
+    const long long bs = row / H;
+    const int s = bs % S;
+    const int b = bs / S;
+    const uint4 a = *reinterpret_cast<const uint4*>(o + b * o_sb + s * o_ss + h * o_sh + part * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(dO + b * do_sb + s * do_ss + h * do_sh + part * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-  for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
-  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
-  float* dq = dq_acc + row * d;
-  for (int c = lane; c < d; c += 32) dq[c] = 0.f;
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = unpack_bf16x2(aw[k]);
+      const float2 y = unpack_bf16x2(gw[k]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+    float4* dq = reinterpret_cast<float4*>(dq_acc + row * d + part * 8);
+    dq[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    dq[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int o2 = group >> 1; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2, 16);
+  if (row < total && part == 0) {
+    const int h = row % H;
+    const long long bs = row / H;
+    delta[(static_cast<long long>(bs / S) * H + h) * S + (bs % S)] = acc;
+  }
 }
 
+// dq (bf16, strided) <- dq_acc (fp32, [B, S, H, d]); 8 elements per thread.
 __global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dq,
                                      long long dq_sb, long long dq_ss, long long dq_sh, int B, int H,
                                      int S, int d) {
-  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;  // pair index
-  const long long total = static_cast<long long>(B) * S * H * d / 2;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long total = static_cast<long long>(B) * S * H * d / 8;
   if (idx >= total) return;
-  const long long e = idx * 2;
+  const long long e = idx * 8;
   const int c = e % d;
   const long long row = e / d;
   const int h = row % H;
   const long long bs = row / H;
   const int s = bs % S;
   const int b = bs / S;
-  const float2 v = *reinterpret_cast<const float2*>(dq_acc + e);
-  *reinterpret_cast<__nv_bfloat162*>(dq + b * dq_sb + s * dq_ss + h * dq_sh + c) = __floats2bfloat162_rn(v.x, v.y);
+  const float4 v0 = reinterpret_cast<const float4*>(dq_acc + e)[0];
+  const float4 v1 = reinterpret_cast<const float4*>(dq_acc + e)[1];
+  uint4 out;
+  out.x = pack_bf16x2(v0.x, v0.y);
+  out.y = pack_bf16x2(v0.z, v0.w);
+  out.z = pack_bf16x2(v1.x, v1.y);
+  out.w = pack_bf16x2(v1.z, v1.w);
+  *reinterpret_cast<uint4*>(dq + b * dq_sb + s * dq_ss + h * dq_sh + c) = out;
 }
 
 static int make_attn_map(CUtensorMap* m, const void* ptr, int d, int S, int H, int B, long long ss,
@@ -859,7 +877,7 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   {
     const long long rows = static_cast<long long>(B) * Sq * Hq;
     const int threads = 256;
-    const long long blocks = (rows * 32 + threads - 1) / threads;
+    const long long blocks = (rows * (d <= 64 ? 8 : 16) + threads - 1) / threads;
     attn_bwd_prep_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(
         static_cast<const __nv_bfloat16*>(o->ptr), static_cast<const __nv_bfloat16*>(dout->ptr), o->stride_b,
         o->stride_s, o->stride_h, dout->stride_b, dout->stride_s, dout->stride_h, delta, dq_acc, B, Hq, Sq, d);
@@ -894,9 +912,9 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   e = cudaGetLastError();
   if (e != cudaSuccess) return 400 + e;
   {
-    const long long pairs = static_cast<long long>(B) * Sq * Hq * d / 2;
+    const long long octets = static_cast<long long>(B) * Sq * Hq * d / 8;
     const int threads = 256;
-    attn_dq_store_kernel<<<static_cast<unsigned>((pairs + threads - 1) / threads), threads, 0, s>>>(
+    attn_dq_store_kernel<<<static_cast<unsigned>((octets + threads - 1) / threads), threads, 0, s>>>(
         dq_acc, static_cast<__nv_bfloat16*>(dq->ptr), dq->stride_b, dq->stride_s, dq->stride_h, B, Hq, Sq, d);
   }
   e = cudaGetLastError();

@@ -209,13 +209,35 @@ __device__ __forceinline__ void tmem_st_wait() {
 }
 
 // ------------------------------------------------------------------- maths --
+// Exact-erf GELU and its derivative with the Abramowitz-Stegun 7.1.26 rational
+// approximation of erf (|error| < 1.5e-7, far below bf16 resolution):
+//   erf(z) = 1 - (a1 t + ... + a5 t^5) exp(-z^2),  t = 1 / (1 + p z),  z >= 0.
+// With z = |x| / sqrt(2) the exponential is exp(-x^2 / 2), which the derivative
+// needs anyway (normal density), so one ex2 serves both.
+__device__ __forceinline__ void gelu_parts(float x, float& cdf, float& dens) {
+  const float ax = fabsf(x);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-0.72134752044448170368f * x * x));  // exp(-x^2/2)
+  float t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.23164190397f, ax, 1.0f)));     // p / sqrt(2)
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(t, poly, 1.421413741f);
+  poly = fmaf(t, poly, -0.284496736f);
+  poly = fmaf(t, poly, 0.254829592f);
+  poly *= t;
+  const float half_erfc = 0.5f * poly * e;          // 0.5 * (1 - erf(|x|/sqrt2))
+  cdf = x >= 0.f ? 1.0f - half_erfc : half_erfc;
+  dens = 0.39894228040143267794f * e;
+}
 __device__ __forceinline__ float gelu_erf_f(float x) {
-  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+  float cdf, dens;
+  gelu_parts(x, cdf, dens);
+  return x * cdf;
 }
 __device__ __forceinline__ float gelu_erf_grad_f(float x) {
-  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752440f));
-  const float pdf = 0.39894228040143267794f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  float cdf, dens;
+  gelu_parts(x, cdf, dens);
+  return fmaf(x, dens, cdf);
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

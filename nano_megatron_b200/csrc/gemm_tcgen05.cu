@@ -17,7 +17,8 @@
 // Structure: persistent CTAs (one per SM), 192 threads:
 //   warp 0      TMA producer (one elected lane), STAGES-deep smem ring
 //   warp 1      TMEM owner + single-thread tcgen05.mma issuer
-//   warps 2..5  epilogue: tcgen05.ld -> registers -> bias/GELU/residual -> global
+//   warps 2..9  epilogue: tcgen05.ld -> registers -> bias/GELU/residual -> global
+//               (two warps per TMEM lane quadrant, each takes half of the columns)
 // Two TMEM accumulator buffers let the epilogue of tile i overlap the main
 // loop of tile i+1.  No cluster launch, no multicast: every CTA loads its own
 // tiles.
@@ -27,7 +28,7 @@ namespace nmb {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
 enum EpilogueMode : int {
   kEpiPlain = 0,   // C = acc (+bias) (+residual) (+C_old)
@@ -91,7 +92,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -188,7 +189,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------ epilogue --
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int quad = warp & 3;          // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;   // which half of the tile's columns this warp drains
     int local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
       const int buf = local & 1;
@@ -201,7 +203,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const bool row_ok = row < M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= N) break;  // uniform across the warp
         uint32_t r[32];
@@ -403,9 +405,11 @@ template <bool A_MN, bool B_MN>
 static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep,
                          int M, int N, int K, int* status, cudaStream_t stream) {
   const int tiles256 = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
-  // Wide tiles halve the operand traffic per FLOP; use them once they still
-  // fill the machine.
-  if (tiles256 >= sm_count() && N >= 256)
+  // A 128 x 128 UMMA reads 8 KiB of operands from shared memory per 64 clocks,
+  // i.e. the full 128 B/clk of the SM, and the TMA writes compete for the same
+  // bandwidth; the 128 x 256 shape needs 25% less per FLOP.  Narrow tiles only
+  // pay when the wide ones would leave most of the machine idle.
+  if (N > 128 && tiles256 * 3 >= sm_count())
     return launch_gemm<256, 4, A_MN, B_MN>(A, lda, B, ldb, ep, M, N, K, status, stream);
   return launch_gemm<128, 6, A_MN, B_MN>(A, lda, B, ldb, ep, M, N, K, status, stream);
 }

@@ -69,6 +69,185 @@ __global__ void norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
   }
 }
 
+// Vector variants: rows of H = 256 * V elements, every lane keeps its 8 * V
+// elements of the row in registers (one 16-byte load per 256-column chunk), so
+// the row is read from memory exactly once.
+template <int V>
+__global__ void norm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                    const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ y,
+                                    float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, float eps,
+                                    int rms) {
+  constexpr int H = 256 * V;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
+    float v[V][8];
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < V; ++c) {
+      const uint4 u = xr[c * 32 + lane];
+      const uint32_t ww[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16x2(ww[k]);
+        v[c][2 * k] = f.x;
+        v[c][2 * k + 1] = f.y;
+        s += f.x + f.y;
+      }
+    }
+    const float mean = rms ? 0.f : warp_sum(s) / H;
+    float sq = 0.f;
+#pragma unroll
+    for (int c = 0; c < V; ++c)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float d = v[c][k] - mean;
+        sq += d * d;
+      }
+    const float rstd = rsqrtf(warp_sum(sq) / H + eps);
+    if (lane == 0) {
+      if (mean_out != nullptr) mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+    uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * H);
+#pragma unroll
+    for (int c = 0; c < V; ++c) {
+      const uint4 gu = __ldg(reinterpret_cast<const uint4*>(w) + c * 32 + lane);
+      const uint32_t gg[4] = {gu.x, gu.y, gu.z, gu.w};
+      uint32_t bb[4] = {0, 0, 0, 0};
+      if (!rms && bias != nullptr) {
+        const uint4 bu = __ldg(reinterpret_cast<const uint4*>(bias) + c * 32 + lane);
+        bb[0] = bu.x; bb[1] = bu.y; bb[2] = bu.z; bb[3] = bu.w;
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 g = unpack_bf16x2(gg[k]);
+        const float2 b2 = unpack_bf16x2(bb[k]);
+        o[k] = pack_bf16x2((v[c][2 * k] - mean) * rstd * g.x + b2.x, (v[c][2 * k + 1] - mean) * rstd * g.y + b2.y);
+      }
+      yr[c * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// dx plus per-block partial sums of dgamma / dbeta: every warp accumulates the
+// column sums of the rows it processes in registers, the block combines its
+// warps in shared memory and writes ONE partial row per block; a second tiny
+// kernel adds the partial rows.  dy and x are read once.
+template <int V>
+__global__ void norm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
+                                    const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                                    float* __restrict__ partial, int rows, int rms) {
+  constexpr int H = 256 * V;
+  extern __shared__ float red[];  // [warps][2][H]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps_per_block = blockDim.x >> 5;
+  float wv[V][8];
+#pragma unroll
+  for (int c = 0; c < V; ++c) {
+    const uint4 gu = __ldg(reinterpret_cast<const uint4*>(w) + c * 32 + lane);
+    const uint32_t gg[4] = {gu.x, gu.y, gu.z, gu.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 g = unpack_bf16x2(gg[k]);
+      wv[c][2 * k] = g.x;
+      wv[c][2 * k + 1] = g.y;
+    }
+  }
+  float dg[V][8], db[V][8];
+#pragma unroll
+  for (int c = 0; c < V; ++c)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) dg[c][k] = db[c][k] = 0.f;
+  for (int row = blockIdx.x * warps_per_block + warp; row < rows; row += gridDim.x * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * H);
+    const float mean = rms ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float xh[V][8], g[V][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < V; ++c) {
+      const uint4 xu = xr[c * 32 + lane];
+      const uint4 gu = gr[c * 32 + lane];
+      const uint32_t xx[4] = {xu.x, xu.y, xu.z, xu.w};
+      const uint32_t gg[4] = {gu.x, gu.y, gu.z, gu.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = unpack_bf16x2(xx[k]);
+        const float2 b = unpack_bf16x2(gg[k]);
+        xh[c][2 * k] = (a.x - mean) * rstd;
+        xh[c][2 * k + 1] = (a.y - mean) * rstd;
+        g[c][2 * k] = b.x;
+        g[c][2 * k + 1] = b.y;
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        dg[c][k] += g[c][k] * xh[c][k];
+        db[c][k] += g[c][k];
+        const float gw = g[c][k] * wv[c][k];
+        s1 += gw;
+        s2 += gw * xh[c][k];
+      }
+    }
+    s1 = rms ? 0.f : warp_sum(s1) / H;
+    s2 = warp_sum(s2) / H;
+    uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * H);
+#pragma unroll
+    for (int c = 0; c < V; ++c) {
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        o[k] = pack_bf16x2(rstd * (g[c][2 * k] * wv[c][2 * k] - s1 - xh[c][2 * k] * s2),
+                           rstd * (g[c][2 * k + 1] * wv[c][2 * k + 1] - s1 - xh[c][2 * k + 1] * s2));
+      dr[c * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  float* mine = red + static_cast<size_t>(warp) * 2 * H;
+#pragma unroll
+  for (int c = 0; c < V; ++c) {
+    float4* g4 = reinterpret_cast<float4*>(mine + (c * 32 + lane) * 8);
+    float4* b4 = reinterpret_cast<float4*>(mine + H + (c * 32 + lane) * 8);
+    g4[0] = make_float4(dg[c][0], dg[c][1], dg[c][2], dg[c][3]);
+    g4[1] = make_float4(dg[c][4], dg[c][5], dg[c][6], dg[c][7]);
+    b4[0] = make_float4(db[c][0], db[c][1], db[c][2], db[c][3]);
+    b4[1] = make_float4(db[c][4], db[c][5], db[c][6], db[c][7]);
+  }
+  __syncthreads();
+  float* prow = partial + static_cast<size_t>(blockIdx.x) * 2 * H;
+  for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) {
+    float acc = 0.f;
+    for (int wv2 = 0; wv2 < warps_per_block; ++wv2) acc += red[static_cast<size_t>(wv2) * 2 * H + i];
+    prow[i] = acc;
+  }
+}
+
+// Sums the per-block partial rows: 32 columns per block, 8 groups of partial
+// rows summed in parallel and combined through shared memory.
+__global__ void norm_bwd_finish_kernel(const float* __restrict__ partial, int n_partial, int H,
+                                       __nv_bfloat16* __restrict__ dgamma, __nv_bfloat16* __restrict__ dbeta) {
+  __shared__ float red[8][32];
+  const int cx = threadIdx.x & 31;
+  const int px = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + cx;  // column in [0, 2H): dgamma then dbeta
+  float acc = 0.f;
+  for (int p = px; p < n_partial; p += 8) acc += partial[static_cast<size_t>(p) * 2 * H + col];
+  red[px][cx] = acc;
+  __syncthreads();
+  if (px == 0) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += red[k][cx];
+    if (col < H) dgamma[col] = __float2bfloat16(s);
+    else if (dbeta != nullptr) dbeta[col - H] = __float2bfloat16(s);
+  }
+}
+
 // dx for one row:  g = dy * w ;  xhat = (x - mean) * rstd
 //   layernorm: dx = rstd * (g - mean(g) - xhat * mean(g * xhat))
 //   rmsnorm  : dx = rstd * (g - xhat * mean(g * xhat))
@@ -122,7 +301,7 @@ __global__ void norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const _
 //   mode 1: out0[c] = sum_r dy[r,c] * xhat[r,c] (dgamma), out1[c] = sum_r dy[r,c] (dbeta)
 // Stage 1 writes partial[split][2][H] (fp32); stage 2 sums the splits and
 // stores / accumulates bf16.
-constexpr int kColSplit = 16;
+constexpr int kColSplit = 64;
 
 __global__ void col_reduce_stage1(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                   const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
@@ -171,7 +350,7 @@ __global__ void col_reduce_stage2(const float* __restrict__ partial, __nv_bfloat
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= H) return;
   float s0 = 0.f, s1 = 0.f;
-#pragma unroll
+#pragma unroll 8
   for (int k = 0; k < kColSplit; ++k) {
     s0 += partial[(static_cast<size_t>(k) * 2) * H + c];
     s1 += partial[(static_cast<size_t>(k) * 2 + 1) * H + c];
@@ -190,6 +369,16 @@ __global__ void col_reduce_stage2(const float* __restrict__ partial, __nv_bfloat
 
 using namespace nmb;
 
+template <int V>
+static void launch_fwd_vec(const void* x, const void* w, const void* bias, void* y, float* mean, float* rstd, int rows,
+                           float eps, int rms, int blocks, cudaStream_t s) {
+  norm_fwd_vec_kernel<V><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+                                               static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(y),
+                                               mean, rstd, rows, eps, rms);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 extern "C" int nmb_norm_fwd(const void* x, const void* w, const void* bias, void* y, float* mean, float* rstd,
                             int rows, int H, float eps, int rms, void* stream) {
   if (rows <= 0) return 0;
@@ -198,6 +387,21 @@ extern "C" int nmb_norm_fwd(const void* x, const void* w, const void* bias, void
   int blocks = (rows + 7) / 8;
   const int cap = sm_count() * 8;
   if (blocks > cap) blocks = cap;
+  if (H % 256 == 0 && H <= 2048 && aligned16(x) && aligned16(w) && aligned16(y) && (bias == nullptr || aligned16(bias))) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (H / 256) {
+      case 1: launch_fwd_vec<1>(x, w, bias, y, mean, rstd, rows, eps, rms, blocks, s); break;
+      case 2: launch_fwd_vec<2>(x, w, bias, y, mean, rstd, rows, eps, rms, blocks, s); break;
+      case 3: launch_fwd_vec<3>(x, w, bias, y, mean, rstd, rows, eps, rms, blocks, s); break;
+      case 4: launch_fwd_vec<4>(x, w, bias, y, mean, rstd, rows, eps, rms, blocks, s); break;
+      case 6: launch_fwd_vec<6>(x, w, bias, y, mean, rstd, rows, eps, rms, blocks, s); break;
+      case 8: launch_fwd_vec<8>(x, w, bias, y, mean, rstd, rows, eps, rms, blocks, s); break;
+      default: goto generic;
+    }
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : 400 + e;
+  }
+generic:
   norm_fwd_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
       static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(y), mean, rstd, rows, H, eps, rms);
@@ -221,7 +425,54 @@ extern "C" int nmb_norm_bwd_dx(const void* dy, const void* x, const void* w, con
   return e == cudaSuccess ? 0 : 400 + e;
 }
 
-// `partial` is fp32 scratch of 2 * 16 * H elements.
+template <int V>
+static int configure_bwd_vec() {
+  cudaError_t e = cudaFuncSetAttribute(norm_bwd_vec_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       8 * 2 * 256 * V * static_cast<int>(sizeof(float)));
+  return e == cudaSuccess ? 0 : 300 + e;
+}
+
+extern "C" int nmb_norm_configure() {
+  return configure_bwd_vec<1>() | configure_bwd_vec<2>() | configure_bwd_vec<3>() | configure_bwd_vec<4>();
+}
+
+template <int V>
+static void launch_bwd_vec(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
+                           float* partial, int rows, int rms, int blocks, cudaStream_t s) {
+  norm_bwd_vec_kernel<V><<<blocks, 256, 8 * 2 * 256 * V * sizeof(float), s>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      mean, rstd, static_cast<__nv_bfloat16*>(dx), partial, rows, rms);
+}
+
+// Fused backward: dx, dgamma, dbeta in one pass over dy and x.  Needs
+// H % 256 == 0, H <= 1024 (register budget) and 16-byte aligned rows; returns
+// -1 when the shape is not covered (callers then use the generic kernels).
+// `partial` is fp32 scratch of kNormBwdBlocks * 2 * H elements.
+constexpr int kNormBwdBlocks = 148;
+extern "C" int nmb_norm_bwd_fused_blocks() { return kNormBwdBlocks; }
+
+extern "C" int nmb_norm_bwd_fused(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                  void* dx, void* dgamma, void* dbeta, float* partial, int rows, int H, int rms,
+                                  void* stream) {
+  if (rows <= 0) return 0;
+  if (H % 256 != 0 || H > 1024 || !aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx)) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int blocks = (rows + 7) / 8;
+  if (blocks > kNormBwdBlocks) blocks = kNormBwdBlocks;
+  switch (H / 256) {
+    case 1: launch_bwd_vec<1>(dy, x, w, mean, rstd, dx, partial, rows, rms, blocks, s); break;
+    case 2: launch_bwd_vec<2>(dy, x, w, mean, rstd, dx, partial, rows, rms, blocks, s); break;
+    case 3: launch_bwd_vec<3>(dy, x, w, mean, rstd, dx, partial, rows, rms, blocks, s); break;
+    case 4: launch_bwd_vec<4>(dy, x, w, mean, rstd, dx, partial, rows, rms, blocks, s); break;
+    default: return -1;
+  }
+  norm_bwd_finish_kernel<<<2 * H / 32, 256, 0, s>>>(partial, blocks, H, static_cast<__nv_bfloat16*>(dgamma),
+                                                    static_cast<__nv_bfloat16*>(dbeta));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+// `partial` is fp32 scratch of 2 * 64 * H elements.
 extern "C" int nmb_col_reduce(const void* dy, int ld, const void* x, const float* mean, const float* rstd,
                               float* partial, void* out0, void* out1, int rows, int H, int mode, int rms,
                               int accumulate, void* stream) {

@@ -33,21 +33,39 @@ class Trainer:
                  loss_fn: Optional[Callable[[Tensor, Tensor], Tensor]] = None) -> None:
         self.model = model
         self.ctx = ctx
+        self.graph_error: Optional[str] = None
         self.ddp = DistributedDataParallel(model, ctx, bucket_cap_mb=bucket_cap_mb)
         self.optimizer = AdamW(model.named_parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         self._loss_fn = loss_fn or model.shifted_cross_entropy
         self.device = next(model.parameters()).device
         on_gpu = self.device.type == "cuda"
         self._want_graph = on_gpu if use_cuda_graph is None else (use_cuda_graph and on_gpu)
+        if self._want_graph and not self._collectives_are_graph_safe():
+            # Library (NCCL) collectives would land inside the capture; that
+            # combination is left eager here.  The peer-memory kernels of this
+            # package are plain kernels and capture like any other.
+            self._want_graph = False
+            self.graph_error = "not captured: the step contains NCCL collectives"
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._graph_warmup = graph_warmup
         self._eager_steps = 0
         self._ids: Optional[Tensor] = None
         self._labels: Optional[Tensor] = None
         self._loss: Optional[Tensor] = None
-        self.graph_error: Optional[str] = None
         #: number of this library's kernels recorded in the captured graph
         self.kernels_in_graph = 0
+
+    def _collectives_are_graph_safe(self) -> bool:
+        ctx = self.ctx
+        if getattr(ctx, "world_size", 1) == 1:
+            return True
+        if ctx.tensor_parallel_size > 1 or ctx.pipeline_parallel_size > 1:
+            return False
+        if ctx.context_parallel_size > 1:
+            from ..distributed import symmetric
+            if symmetric.workspace_for(ctx.context_parallel_group) is None:
+                return False
+        return all(b.fused_reduce is not None for b in self.ddp._buckets)
 
     # ------------------------------------------------------------------ step --
     def _step_body(self) -> Tensor:

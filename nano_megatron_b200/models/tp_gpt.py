@@ -215,10 +215,9 @@ class TPMLP(nn.Module):
 
     def forward(self, x: Tensor, *, residual: Optional[Tensor] = None) -> Tensor:
         if self.config.gated_linear_unit:
-            h = OF.swiglu(self.fc1(x))
-        else:
-            h = self.fc1(x, gelu=True)
-        return self.fc2(h, residual=residual)
+            return self.fc2(OF.swiglu(self.fc1(x)), residual=residual)
+        pre, act = self.fc1(x, split_gelu=True)
+        return self.fc2(act, residual=residual, gelu_pre=pre)
 
 
 class TPTransformerBlock(nn.Module):

@@ -26,7 +26,7 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from . import kernels
-from .gemm import EPI_GELU, EPI_PLAIN, gemm_bf16, gemm_supported
+from .gemm import EPI_DGELU, EPI_GELU, EPI_PLAIN, gemm_bf16, gemm_supported
 
 
 def use_native(t: Tensor) -> bool:
@@ -95,7 +95,87 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db, d_res, None
 
 
-def _native_linear_ok(x: Tensor, weight: Tensor) -> bool:
+def _rows(t: Tensor, width: int) -> Tensor:
+    t2 = t.reshape(-1, width)
+    if t2.stride(-1) != 1 or (t2.stride(0) % 8) != 0:
+        t2 = t2.contiguous()
+    return t2
+
+
+class _LinearGeluSplitFn(torch.autograd.Function):
+    """First MLP GEMM: returns the pre-activation (differentiable) and its GELU
+    (a side output written by the same epilogue)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor]):
+        x2 = _rows(x, x.shape[-1])
+        n = weight.shape[0]
+        pre = torch.empty((x2.shape[0], n), dtype=torch.bfloat16, device=x.device)
+        act = gemm_bf16(x2, weight, bias=bias, mode=EPI_GELU, aux_out=pre)
+        ctx.save_for_backward(x2, weight)
+        ctx.params = (weight, bias)
+        ctx.in_shape = x.shape
+        out_shape = (*x.shape[:-1], n)
+        act = act.view(out_shape)
+        ctx.mark_non_differentiable(act)
+        return pre.view(out_shape), act
+
+    @staticmethod
+    def backward(ctx, dpre: Tensor, _dact):
+        x2, weight = ctx.saved_tensors
+        w_param, b_param = ctx.params
+        dz = _rows(dpre, weight.shape[0])
+        dx = gemm_bf16(dz, weight, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
+        dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dz, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        db = None
+        if b_param is not None:
+            db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dz, out=out, accumulate=acc))
+        return dx, dw, db
+
+
+class _LinearFromGeluFn(torch.autograd.Function):
+    """Second MLP GEMM.  Its input is ``gelu(pre)`` (already computed); the
+    gradient it returns is with respect to ``pre``: GELU' is applied in the
+    epilogue of the dgrad GEMM, so no separate GELU-backward kernel runs."""
+
+    @staticmethod
+    def forward(ctx, pre: Tensor, act: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor]):
+        k = act.shape[-1]
+        a2 = _rows(act, k)
+        n = weight.shape[0]
+        res2 = residual.reshape(-1, n) if residual is not None else None
+        y = gemm_bf16(a2, weight, bias=bias, residual=res2)
+        ctx.save_for_backward(_rows(pre, k), a2, weight)
+        ctx.params = (weight, bias)
+        ctx.has_res = residual is not None
+        ctx.pre_shape = pre.shape
+        return y.view(*act.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        pre2, a2, weight = ctx.saved_tensors
+        w_param, b_param = ctx.params
+        dy2 = _rows(dy, weight.shape[0])
+        dpre = gemm_bf16(dy2, weight, b_mn=True, mode=EPI_DGELU, aux_in=pre2).view(ctx.pre_shape)
+        dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dy2, a2, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        db = None
+        if b_param is not None:
+            db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dy2, out=out, accumulate=acc))
+        return dpre, None, dw, db, (dy if ctx.has_res else None)
+
+
+def linear_gelu_split(x: Tensor, weight: Tensor, bias: Optional[Tensor]) -> tuple[Tensor, Tensor]:
+    """``pre = x W^T + b`` and ``gelu(pre)`` from one GEMM (native path only)."""
+    return _LinearGeluSplitFn.apply(x, weight, bias)
+
+
+def linear_from_gelu(pre: Tensor, act: Tensor, weight: Tensor, bias: Optional[Tensor],
+                     residual: Optional[Tensor] = None) -> Tensor:
+    """``act W^T + b (+ residual)`` where ``act = gelu(pre)``; backward flows into ``pre``."""
+    return _LinearFromGeluFn.apply(pre, act, weight, bias, residual)
+
+
+def native_linear_ok(x: Tensor, weight: Tensor) -> bool:
     k = x.shape[-1]
     n = weight.shape[0]
     return use_native(x) and weight.dtype == torch.bfloat16 and weight.is_contiguous() and \
@@ -106,7 +186,7 @@ def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, *, residual
            gelu: bool = False) -> Tensor:
     """``act(x @ weight.T + bias) + residual`` (``gelu`` and ``residual`` are exclusive)."""
     assert not (gelu and residual is not None)
-    if _native_linear_ok(x, weight):
+    if native_linear_ok(x, weight):
         return _LinearFn.apply(x, weight, bias, residual, gelu)
     # Rows that are not multiples of 16 bytes cannot be described to TMA; such
     # (toy) shapes use the PyTorch expression below.

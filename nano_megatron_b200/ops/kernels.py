@@ -26,7 +26,7 @@ def _col_scratch(device: torch.device, h: int) -> torch.Tensor:
     key = (device.index or 0, h)
     buf = _scratch.get(key)
     if buf is None:
-        buf = torch.empty(2 * 16 * h, dtype=torch.float32, device=device)
+        buf = torch.empty(2 * 64 * h, dtype=torch.float32, device=device)
         _scratch[key] = buf
     return buf
 
@@ -46,12 +46,33 @@ def norm_fwd(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: f
     return y, mean, rstd
 
 
+_norm_partial: dict[tuple[int, int], torch.Tensor] = {}
+
+
 def norm_bwd(dy, x, w, mean, rstd, rms: bool, dx_add: Optional[torch.Tensor] = None, want_bias: bool = True):
     dy, x = _bf16(dy), _bf16(x)
     h = x.shape[-1]
     rows = x.numel() // h
     dx = torch.empty_like(x)
     lib = native.lib()
+    if dx_add is None and h % 256 == 0 and h <= 1024:
+        # one pass over dy and x: dx plus the column sums for dgamma / dbeta
+        key = (x.device.index or 0, h)
+        partial = _norm_partial.get(key)
+        if partial is None:
+            partial = torch.empty(lib.nmb_norm_bwd_fused_blocks() * 2 * h, dtype=torch.float32, device=x.device)
+            _norm_partial[key] = partial
+        dw = torch.empty(h, dtype=torch.bfloat16, device=x.device)
+        db = torch.empty(h, dtype=torch.bfloat16, device=x.device) if want_bias else None
+        rc = lib.nmb_norm_bwd_fused(native.ptr(dy), native.ptr(x), native.ptr(_bf16(w)), native.ptr(mean),
+                                    native.ptr(rstd), native.ptr(dx), native.ptr(dw), native.ptr(db),
+                                    native.ptr(partial), c_int(rows), c_int(h), c_int(int(rms)),
+                                    native.stream_ptr(x.device))
+        if rc == 0:
+            native.launches += 2
+            return dx, dw, db
+        if rc != -1:
+            native.check_rc(rc, "nmb_norm_bwd_fused")
     rc = lib.nmb_norm_bwd_dx(native.ptr(dy), native.ptr(x), native.ptr(_bf16(w)), native.ptr(mean), native.ptr(rstd),
                              native.ptr(None if dx_add is None else _bf16(dx_add)), native.ptr(dx), c_int(rows),
                              c_int(h), c_int(int(rms)), native.stream_ptr(x.device))

@@ -315,11 +315,17 @@ class ColumnParallelLinear(nn.Module):
         self.buffer_manager = CommunicationBuffer()
         self.sequence_parallel = sequence_parallel
 
-    def forward(self, x: Tensor, *, gelu: bool = False) -> Tensor:
+    def forward(self, x: Tensor, *, gelu: bool = False, split_gelu: bool = False):
+        """``split_gelu`` returns ``(pre_activation, gelu(pre_activation))`` so that
+        the following row-parallel linear can fold GELU' into its dgrad GEMM."""
         if self.sequence_parallel:
             x = gather_from_sequence_parallel_region(x, self.group, self.backend, self.tp_rank, self.tp_size)
         elif self.tp_size > 1:
             x = _CopyToTPRegion.apply(x, self.group, self.backend, self.buffer_manager)
+        if split_gelu:
+            if OF.native_linear_ok(x, self.weight):
+                return OF.linear_gelu_split(x, self.weight, self.bias)
+            return None, OF.linear(x, self.weight, self.bias, gelu=True)
         return OF.linear(x, self.weight, self.bias, gelu=gelu)
 
 
@@ -341,11 +347,16 @@ class RowParallelLinear(nn.Module):
         if sequence_parallel and self.bias is not None:
             register_sequence_parallel_grad_allreduce(self.bias, group, backend)
 
-    def forward(self, x: Tensor, *, residual: Optional[Tensor] = None) -> Tensor:
+    def forward(self, x: Tensor, *, residual: Optional[Tensor] = None, gelu_pre: Optional[Tensor] = None) -> Tensor:
+        """``gelu_pre``: ``x`` is ``gelu(gelu_pre)`` (from ``split_gelu``); the backward
+        then returns the gradient of ``gelu_pre``."""
+        fused = gelu_pre is not None and OF.native_linear_ok(x, self.weight)
         if self.tp_size == 1:
             # Nothing to reduce: bias and residual ride in the GEMM epilogue.
+            if fused:
+                return OF.linear_from_gelu(gelu_pre, x, self.weight, self.bias, residual)
             return OF.linear(x, self.weight, self.bias, residual=residual)
-        out = OF.linear(x, self.weight, None)
+        out = OF.linear_from_gelu(gelu_pre, x, self.weight, None) if fused else OF.linear(x, self.weight, None)
         if self.sequence_parallel:
             out = reduce_scatter_to_sequence_parallel_region(out, self.group, self.backend, self.tp_rank, self.tp_size)
         else:
