@@ -23,26 +23,9 @@
 
 namespace nmb {
 
-constexpr int kMaxRanks = 8;
-constexpr int kMaxBlocks = 256;
-constexpr int kChannels = 4;
-
 struct PeerPtrs {
   void* p[kMaxRanks];
 };
-
-__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ uint32_t* pad_slot(void* pad, int channel, int block, int rank) {
-  return static_cast<uint32_t*>(pad) + (static_cast<size_t>(channel) * kMaxBlocks + block) * kMaxRanks + rank;
-}
 
 // Block-level barrier with the same block index on every rank of the group.
 // `budget` in clock cycles.  Returns false (for the whole block) on a timeout.

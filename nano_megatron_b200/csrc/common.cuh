@@ -208,6 +208,43 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// ----------------------------------------------------- cross-GPU signalling --
+__device__ __forceinline__ void st_release_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+// Generic-proxy writes to global memory become visible to later TMA (async
+// proxy) reads, and vice versa.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Signal-pad geometry shared by every peer-memory kernel.
+constexpr int kMaxRanks = 8;
+constexpr int kMaxBlocks = 256;
+constexpr int kChannels = 4;
+__device__ __forceinline__ uint32_t* pad_slot(void* pad, int channel, int block, int rank) {
+  return static_cast<uint32_t*>(pad) + (static_cast<size_t>(channel) * kMaxBlocks + block) * kMaxRanks + rank;
+}
+// Bounded wait until *flag >= want (signed distance, so counters may wrap).
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t want, long long budget) {
+  const long long t0 = clock64();
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - want) < 0) {
+    if (clock64() - t0 > budget) return false;
+  }
+  return true;
+}
+
 // ------------------------------------------------------------------- maths --
 // Exact-erf GELU and its derivative with the Abramowitz-Stegun 7.1.26 rational
 // approximation of erf (|error| < 1.5e-7, far below bf16 resolution):

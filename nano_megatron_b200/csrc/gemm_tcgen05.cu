@@ -24,6 +24,8 @@
 // tiles.
 #include "common.cuh"
 
+#include <string.h>
+
 namespace nmb {
 
 constexpr int kBM = 128;
@@ -51,6 +53,48 @@ struct GemmEpilogue {
   float alpha;              // scale applied to the accumulator first
 };
 
+// Collective fused into the GEMM (both optional, normally one at a time).
+//
+//  * all-gather of A (sequence-parallel input): A's rows are sharded over the
+//    ranks by sequence position.  The last `ag_copy_ctas` CTAs of the launch do
+//    not compute: they pull the peers' shards over NVLink into this rank's full
+//    A buffer, 128-row tile by tile, and publish a ready flag per tile; the GEMM
+//    CTAs walk the tiles local-shard-first and wait for a tile's flag before
+//    issuing its first TMA load, so the transfer hides behind the math.  Every
+//    remote tile crosses NVLink once and is then read from local memory.
+//  * reduce-scatter / all-reduce of C: the epilogue stores each partial tile
+//    straight into the owner rank's staging slot [my_rank] (peer stores); when
+//    every rank has stored all its tiles (one flag round), each rank sums the
+//    slots of its rows, adds bias / residual and writes the result -- to its own
+//    shard (reduce-scatter) or to every rank's output (all-reduce).
+struct FusedComm {
+  const void* ag_src[kMaxRanks];
+  void* ag_dst;
+  uint32_t* ag_ready;
+  int ag_copy_ctas;
+  int rs_mode;  // 0 off, 1 reduce-scatter, 2 all-reduce
+  void* rs_stage[kMaxRanks];
+  void* rs_out[kMaxRanks];
+  const __nv_bfloat16* rs_bias;
+  const __nv_bfloat16* rs_residual;
+  void* pads[kMaxRanks];
+  uint32_t* epochs;    // [kChannels][kMaxBlocks] device-side epoch counters
+  uint32_t* counters;  // two zero-initialised words for the intra-GPU arrival counts
+  int channel;
+  int rank, n_ranks;
+  int seq_len, shard_len, rows_per_rank;
+  long long budget;
+};
+
+// Rows are [batch][sequence]; a sequence is cut into n_ranks contiguous shards.
+__device__ __forceinline__ int row_owner(const FusedComm& fc, int row) { return (row % fc.seq_len) / fc.shard_len; }
+__device__ __forceinline__ int row_local(const FusedComm& fc, int row) {
+  return (row / fc.seq_len) * fc.shard_len + (row % fc.seq_len) % fc.shard_len;
+}
+__device__ __forceinline__ int row_global(const FusedComm& fc, int owner, int local) {
+  return (local / fc.shard_len) * fc.seq_len + owner * fc.shard_len + local % fc.shard_len;
+}
+
 template <int BN, int STAGES>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
@@ -61,11 +105,171 @@ struct GemmSmem {
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
 };
 
+// Copy CTA of the fused all-gather: pulls remote 128-row tiles of A into the
+// local full buffer and publishes one ready flag per tile.
+__device__ void gather_copy_role(const FusedComm& fc, int M, int K, int copy_idx, int* status) {
+  __shared__ uint32_t epoch_s;
+  __shared__ int ok_s;
+  uint32_t* chan_epoch = fc.epochs + fc.channel * kMaxBlocks;
+  if (threadIdx.x == 0) {
+    epoch_s = chan_epoch[0] + 1;
+    ok_s = 1;
+  }
+  __syncthreads();
+  const uint32_t e = epoch_s;
+  // Peers' shards are complete once their copy CTA of the same index got here
+  // (it runs after everything earlier in that rank's stream).
+  if (threadIdx.x < fc.n_ranks) {
+    __threadfence_system();
+    st_release_sys(pad_slot(fc.pads[threadIdx.x], fc.channel, 1 + copy_idx, fc.rank), e);
+    if (!wait_flag_sys(pad_slot(fc.pads[fc.rank], fc.channel, 1 + copy_idx, threadIdx.x), e, fc.budget)) {
+      report_status(status, kPeerTimeout, 6);
+      ok_s = 0;
+    }
+  }
+  __syncthreads();
+  const int tiles_m = M / kBM;
+  const int tpc = fc.shard_len / kBM;
+  const int nb = M / fc.seq_len;
+  const int per_owner = nb * tpc;
+  const int remote = (fc.n_ranks - 1) * per_owner;
+  const size_t row_bytes = static_cast<size_t>(K) * 2;
+  const int vec_per_tile = static_cast<int>(kBM * row_bytes / 16);
+  for (int i = copy_idx; i < remote; i += fc.ag_copy_ctas) {
+    const int k = 1 + i / per_owner;  // distance from my rank
+    const int rem = i % per_owner;
+    const int owner = (fc.rank + k) % fc.n_ranks;
+    const int m_blk = ((rem / tpc) * fc.seq_len + owner * fc.shard_len) / kBM + rem % tpc;
+    if (ok_s) {
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(fc.ag_src[owner]) +
+                                                        static_cast<size_t>(m_blk) * kBM * row_bytes);
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(fc.ag_dst) + static_cast<size_t>(m_blk) * kBM * row_bytes);
+      constexpr int U = 4;
+      for (int base = threadIdx.x; base < vec_per_tile; base += blockDim.x * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (base + u * static_cast<int>(blockDim.x) < vec_per_tile) v[u] = src[base + u * blockDim.x];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (base + u * static_cast<int>(blockDim.x) < vec_per_tile) dst[base + u * blockDim.x] = v[u];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      fence_proxy_async_all();
+      // even after a failed wait the flag is published so that no GEMM CTA spins
+      st_release_gpu(&fc.ag_ready[m_blk], e);
+    }
+  }
+  (void)tiles_m;
+  // Closing round: no peer is still reading this rank's shard when a later
+  // kernel overwrites it.  (The channel epoch itself is advanced by a separate
+  // one-thread kernel after this launch, once every CTA has read it.)
+  __syncthreads();
+  if (threadIdx.x < fc.n_ranks) {
+    __threadfence_system();
+    st_release_sys(pad_slot(fc.pads[threadIdx.x], fc.channel, 1 + copy_idx, fc.rank), e + 1);
+    if (!wait_flag_sys(pad_slot(fc.pads[fc.rank], fc.channel, 1 + copy_idx, threadIdx.x), e + 1, fc.budget))
+      report_status(status, kPeerTimeout, 7);
+  }
+}
+
+// Second half of GEMM -> reduce-scatter / all-reduce, run by every GEMM CTA
+// after its last tile.
+__device__ void reduce_phase(const FusedComm& fc, int n_ctas, int N, int* status) {
+  __shared__ uint32_t epoch_s;
+  __shared__ int ok_s;
+  uint32_t* chan_epoch = fc.epochs + fc.channel * kMaxBlocks;
+  if (threadIdx.x == 0) {
+    epoch_s = chan_epoch[0];
+    ok_s = 1;
+  }
+  __syncthreads();  // also: this CTA's tile stores precede the fence below
+  const uint32_t e = epoch_s + 1;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned arrived = atomicAdd(&fc.counters[0], 1u);
+    if (arrived == static_cast<unsigned>(n_ctas) - 1) {
+      // last CTA of this GPU: every tile of this rank has been stored
+      fc.counters[0] = 0;
+      __threadfence_system();
+      for (int p = 0; p < fc.n_ranks; ++p) st_release_sys(pad_slot(fc.pads[p], fc.channel, 0, fc.rank), e);
+    }
+  }
+  if (threadIdx.x < fc.n_ranks) {
+    if (!wait_flag_sys(pad_slot(fc.pads[fc.rank], fc.channel, 0, threadIdx.x), e, fc.budget)) {
+      report_status(status, kPeerTimeout, 8);
+      ok_s = 0;
+    }
+  }
+  __syncthreads();
+  if (ok_s) {
+    const long long slot_vecs = static_cast<long long>(fc.rows_per_rank) * N / 8;
+    const int row_vecs = N / 8;
+    const uint4* stage = static_cast<const uint4*>(fc.rs_stage[fc.rank]);
+    for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < slot_vecs;
+         v += static_cast<long long>(n_ctas) * blockDim.x) {
+      float acc[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+      auto add = [&](const uint4& u) {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = unpack_bf16x2(w[k]);
+          acc[2 * k] += f.x;
+          acc[2 * k + 1] += f.y;
+        }
+      };
+      for (int s2 = 0; s2 < fc.n_ranks; ++s2) add(stage[s2 * slot_vecs + v]);
+      const int local = static_cast<int>(v / row_vecs);
+      const int cv = static_cast<int>(v % row_vecs);
+      if (fc.rs_bias != nullptr) add(reinterpret_cast<const uint4*>(fc.rs_bias)[cv]);
+      uint4 o;
+      if (fc.rs_mode == 1) {
+        if (fc.rs_residual != nullptr) add(reinterpret_cast<const uint4*>(fc.rs_residual)[v]);
+        o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
+        static_cast<uint4*>(fc.rs_out[fc.rank])[v] = o;
+      } else {
+        const long long gv = static_cast<long long>(row_global(fc, fc.rank, local)) * row_vecs + cv;
+        if (fc.rs_residual != nullptr) add(reinterpret_cast<const uint4*>(fc.rs_residual)[gv]);
+        o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
+        for (int p = 0; p < fc.n_ranks; ++p) static_cast<uint4*>(fc.rs_out[(fc.rank + p) % fc.n_ranks])[gv] = o;
+      }
+    }
+  }
+  // Closing round: (all-reduce) every rank's rows have landed everywhere.  The
+  // channel epoch is advanced by a one-thread kernel after this launch.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const unsigned arrived = atomicAdd(&fc.counters[1], 1u);
+    if (arrived == static_cast<unsigned>(n_ctas) - 1) {
+      fc.counters[1] = 0;
+      __threadfence_system();
+      for (int p = 0; p < fc.n_ranks; ++p) st_release_sys(pad_slot(fc.pads[p], fc.channel, 0, fc.rank), e + 1);
+    }
+  }
+  if (fc.rs_mode == 2 && threadIdx.x < fc.n_ranks) {
+    if (!wait_flag_sys(pad_slot(fc.pads[fc.rank], fc.channel, 0, threadIdx.x), e + 1, fc.budget))
+      report_status(status, kPeerTimeout, 9);
+  }
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 GemmEpilogue ep, int M, int N, int K, int* status) {
+                 GemmEpilogue ep, const __grid_constant__ FusedComm fc, int M, int N, int K, int* status) {
   using L = GemmSmem<BN, STAGES>;
+  const int n_gemm_ctas = gridDim.x - fc.ag_copy_ctas;
+  if (static_cast<int>(blockIdx.x) >= n_gemm_ctas) {
+    gather_copy_role(fc, M, K, blockIdx.x - n_gemm_ctas, status);
+    return;
+  }
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // SWIZZLE_128B operands need 1024-byte aligned stage bases.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -84,6 +288,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + kBK - 1) / kBK;
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: powers of two
+  const bool gathered = fc.ag_copy_ctas > 0;
+  // tile -> (m block, n block).  Plain GEMM: m fastest.  Gathered A: all n
+  // blocks of an m block together, m blocks ordered local shard first, then the
+  // peers by distance, so the first waves need no remote data.
+  auto tile_coords = [&](int tile, int& m_blk, int& n_blk, int& owner) {
+    if (!gathered) {
+      m_blk = tile % tiles_m;
+      n_blk = tile / tiles_m;
+      owner = fc.rank;
+      return;
+    }
+    const int i_m = tile / tiles_n;
+    n_blk = tile % tiles_n;
+    const int tpc = fc.shard_len / kBM;           // m tiles per (batch, owner) chunk
+    const int nb = M / fc.seq_len;
+    const int k = i_m / (nb * tpc);
+    const int rem = i_m % (nb * tpc);
+    owner = (fc.rank + k) % fc.n_ranks;
+    m_blk = ((rem / tpc) * fc.seq_len + owner * fc.shard_len) / kBM + rem % tpc;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -114,9 +338,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * kBM;
-        const int n0 = (tile / tiles_m) * BN;
+      uint32_t ag_epoch = 0;
+      if (gathered) ag_epoch = fc.epochs[fc.channel * kMaxBlocks + 0] + 1;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += n_gemm_ctas) {
+        int m_blk, n_blk, owner;
+        tile_coords(tile, m_blk, n_blk, owner);
+        const int m0 = m_blk * kBM;
+        const int n0 = n_blk * BN;
+        if (gathered && owner != fc.rank) {
+          // rows of this tile are being copied in by the copy CTAs
+          const long long t0 = clock64();
+          while (static_cast<int32_t>(ld_acquire_gpu(&fc.ag_ready[m_blk]) - ag_epoch) < 0) {
+            if (*abort_flag != 0 || clock64() - t0 > fc.budget) {
+              report_status(status, kPeerTimeout, 5);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_all();
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, 1)) {
             ok = false;
@@ -154,7 +396,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += n_gemm_ctas, ++local) {
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag, status, 2)) break;
@@ -192,11 +434,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quad = warp & 3;          // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;   // which half of the tile's columns this warp drains
     int local = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < num_tiles; tile += n_gemm_ctas, ++local) {
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      const int m0 = (tile % tiles_m) * kBM;
-      const int n0 = (tile / tiles_m) * BN;
+      int m_blk, n_blk, owner_unused;
+      tile_coords(tile, m_blk, n_blk, owner_unused);
+      const int m0 = m_blk * kBM;
+      const int n0 = n_blk * BN;
       if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag, status, 4)) break;
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
@@ -292,8 +536,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               cp[q] = o;
             }
           } else {
-            uint4* cp = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(ep.c) +
-                                                 static_cast<size_t>(row) * ep.ldc + col0);
+            __nv_bfloat16* c_row = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc;
+            if (fc.rs_mode != 0) {
+              // partial tile -> slot [my rank] of the owner's staging buffer
+              const int owner = row_owner(fc, row);
+              c_row = static_cast<__nv_bfloat16*>(fc.rs_stage[owner]) +
+                      (static_cast<size_t>(fc.rank) * fc.rows_per_rank + row_local(fc, row)) * N;
+            }
+            uint4* cp = reinterpret_cast<uint4*>(c_row + col0);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               if (ep.accumulate) {
@@ -359,11 +609,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (fc.rs_mode != 0 && *abort_flag == 0) reduce_phase(fc, n_gemm_ctas, N, status);
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_gemm(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, int M,
-                       int N, int K, int* status, cudaStream_t stream) {
+static int launch_gemm(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
+                       int M, int N, int K, int* status, cudaStream_t stream) {
   using L = GemmSmem<BN, STAGES>;
   CUtensorMap ta, tb;
   int rc;
@@ -395,14 +646,19 @@ static int launch_gemm(const void* A, int lda, const void* B, int ldb, const Gem
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
   const int smem_bytes = L::kTotal + 1024;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kGemmThreads, smem_bytes, stream>>>(ta, tb, ep, M, N, K, status);
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (fc.ag_copy_ctas > 0) {
+    // the copy CTAs take SMs of their own; everything must be co-resident
+    const int compute = sm_count() - fc.ag_copy_ctas;
+    grid = (tiles < compute ? tiles : compute) + fc.ag_copy_ctas;
+  }
+  kern<<<grid, kGemmThreads, smem_bytes, stream>>>(ta, tb, ep, fc, M, N, K, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
 
 template <bool A_MN, bool B_MN>
-static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep,
+static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
                          int M, int N, int K, int* status, cudaStream_t stream) {
   const int tiles256 = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
   // A 128 x 128 UMMA reads 8 KiB of operands from shared memory per 64 clocks,
@@ -410,9 +666,11 @@ static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const G
   // bandwidth; the 128 x 256 shape needs 25% less per FLOP.  Narrow tiles only
   // pay when the wide ones would leave most of the machine idle.
   if (N > 128 && tiles256 * 3 >= sm_count())
-    return launch_gemm<256, 4, A_MN, B_MN>(A, lda, B, ldb, ep, M, N, K, status, stream);
-  return launch_gemm<128, 6, A_MN, B_MN>(A, lda, B, ldb, ep, M, N, K, status, stream);
+    return launch_gemm<256, 4, A_MN, B_MN>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
+  return launch_gemm<128, 6, A_MN, B_MN>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
 }
+
+__global__ void epoch_advance_kernel(uint32_t* epoch, uint32_t by) { *epoch += by; }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int configure_gemm() {
@@ -445,11 +703,10 @@ extern "C" int nmb_gemm_configure() {
 // dimensions are in elements and must be multiples of 8 (TMA: 16-byte pitch);
 // base pointers must be 16-byte aligned.  Returns 0 or a launch error code;
 // device-side timeouts are reported through `status`.
-extern "C" int nmb_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn,
-                             void* C, int ldc, int M, int N, int K, const void* bias,
-                             const void* residual, int ldr, void* aux_out, const void* aux_in,
-                             int ld_aux, int mode, int accumulate, int out_f32, float alpha,
-                             int* status, void* stream) {
+static int gemm_entry(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc, int M,
+                      int N, int K, const void* bias, const void* residual, int ldr, void* aux_out,
+                      const void* aux_in, int ld_aux, int mode, int accumulate, int out_f32, float alpha,
+                      const nmb::FusedComm& fc, int* status, void* stream) {
   using namespace nmb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   (void)cudaGetLastError();  // a stale error of this host thread is not ours to report
@@ -468,17 +725,58 @@ extern "C" int nmb_gemm_bf16(const void* A, int lda, int a_mn, const void* B, in
   ep.accumulate = accumulate;
   ep.out_f32 = out_f32;
   ep.alpha = alpha;
-  // The vector epilogue needs 16-byte aligned rows; otherwise every chunk is
-  // treated as ragged by shrinking nothing here and letting the kernel fall
-  // back per chunk -- so require alignment up front instead.
   const int celt = out_f32 ? 4 : 8;
-  if ((ldc % celt) != 0 || (reinterpret_cast<uintptr_t>(C) & 15)) return kBadArgument;
+  if (fc.rs_mode == 0 && ((ldc % celt) != 0 || (reinterpret_cast<uintptr_t>(C) & 15))) return kBadArgument;
   if (residual != nullptr && ((ldr % 8) != 0 || (reinterpret_cast<uintptr_t>(residual) & 15))) return kBadArgument;
   if ((aux_out != nullptr || aux_in != nullptr) && (ld_aux % 8) != 0) return kBadArgument;
   if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15)) return kBadArgument;
+  if (fc.rs_mode != 0 || fc.ag_copy_ctas > 0) {
+    // fused collectives: whole 128-row tiles per shard, whole 32-column chunks
+    if (fc.n_ranks < 2 || fc.n_ranks > kMaxRanks || fc.shard_len % kBM != 0 || M % fc.seq_len != 0 ||
+        fc.seq_len != fc.shard_len * fc.n_ranks || N % 32 != 0 || out_f32 || accumulate)
+      return kBadArgument;
+    if (fc.rs_mode != 0 && (bias != nullptr || residual != nullptr || mode != kEpiPlain)) return kBadArgument;
+    if (fc.ag_copy_ctas > 0 && (a_mn || fc.ag_copy_ctas >= sm_count() / 2)) return kBadArgument;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (!a_mn && !b_mn) return dispatch_tile<false, false>(A, lda, B, ldb, ep, M, N, K, status, s);
-  if (!a_mn && b_mn) return dispatch_tile<false, true>(A, lda, B, ldb, ep, M, N, K, status, s);
-  if (a_mn && b_mn) return dispatch_tile<true, true>(A, lda, B, ldb, ep, M, N, K, status, s);
-  return dispatch_tile<true, false>(A, lda, B, ldb, ep, M, N, K, status, s);
+  if (!a_mn && !b_mn) return dispatch_tile<false, false>(A, lda, B, ldb, ep, fc, M, N, K, status, s);
+  if (!a_mn && b_mn) return dispatch_tile<false, true>(A, lda, B, ldb, ep, fc, M, N, K, status, s);
+  if (a_mn && b_mn) return dispatch_tile<true, true>(A, lda, B, ldb, ep, fc, M, N, K, status, s);
+  return dispatch_tile<true, false>(A, lda, B, ldb, ep, fc, M, N, K, status, s);
 }
+
+// C[M,N] = epilogue(alpha * A B^T).  `a_mn` / `b_mn` say that the operand is
+// stored with its M/N index contiguous (i.e. as [K, M] / [K, N]).  Leading
+// dimensions are in elements and must be multiples of 8 (TMA: 16-byte pitch);
+// base pointers must be 16-byte aligned.  Returns 0 or a launch error code;
+// device-side timeouts are reported through `status`.
+extern "C" int nmb_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn,
+                             void* C, int ldc, int M, int N, int K, const void* bias,
+                             const void* residual, int ldr, void* aux_out, const void* aux_in,
+                             int ld_aux, int mode, int accumulate, int out_f32, float alpha,
+                             int* status, void* stream) {
+  nmb::FusedComm fc;
+  memset(&fc, 0, sizeof(fc));
+  return gemm_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, bias, residual, ldr, aux_out, aux_in, ld_aux, mode,
+                    accumulate, out_f32, alpha, fc, status, stream);
+}
+
+// The same GEMM with a collective fused in (see FusedComm).  `comm` has the
+// layout of nmb::FusedComm; after the launch a one-thread kernel advances the
+// channel's epoch counter by two.
+extern "C" int nmb_gemm_bf16_fused(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C,
+                                   int ldc, int M, int N, int K, const void* bias, void* aux_out,
+                                   int mode, float alpha, const void* comm, int* status, void* stream) {
+  const nmb::FusedComm* fc = static_cast<const nmb::FusedComm*>(comm);
+  const bool rs = fc->rs_mode != 0;  // bias / residual are applied by the reduce phase then
+  int rc = gemm_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, rs ? nullptr : bias, nullptr, 0,
+                      rs ? nullptr : aux_out, nullptr, N, rs ? nmb::kEpiPlain : mode, 0, 0, alpha, *fc, status,
+                      stream);
+  if (rc != 0) return rc;
+  nmb::epoch_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+      fc->epochs + fc->channel * nmb::kMaxBlocks, 2u);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
+}
+
+extern "C" int nmb_fused_comm_size() { return static_cast<int>(sizeof(nmb::FusedComm)); }

@@ -175,4 +175,6 @@ def enable_symmetric_memory(ctx: Any) -> dict[str, SymmetricWorkspace]:
             ws = SymmetricWorkspace(group)
             symmetric.register_workspace(group, ws)
             made[name] = ws
+    from ..ops import fused_tp
+    fused_tp.ENABLED = ctx.pipeline_parallel_size == 1
     return made

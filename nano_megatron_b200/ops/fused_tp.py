@@ -1,0 +1,265 @@
+"""GEMMs with the tensor/sequence-parallel collective fused into the kernel.
+
+Sequence-parallel Megatron layers pair every GEMM with a collective: all-gather
+before a column-parallel GEMM, reduce-scatter after a row-parallel one, and the
+mirror images in backward.  The reference issues them as separate blocking NCCL
+calls around ``F.linear`` (nano_megatron/parallel/mappings.py:109-163,408-463).
+Here each pair is ONE launch of the tcgen05 GEMM (``csrc/gemm_tcgen05.cu``,
+``FusedComm``) working on symmetric memory:
+
+* ``allgather_gemm``      -- copy CTAs pull the peers' sequence shards into the
+  local full buffer tile by tile while the compute CTAs start on the local
+  shard; a tile's TMA loads wait for its ready flag;
+* ``gemm_reduce_scatter`` -- the epilogue stores every partial tile into the
+  owner rank's staging slot over NVLink; after one flag round each rank sums
+  the slots of its rows and adds bias / residual.
+
+The two autograd functions below give the sequence-parallel column / row linear
+their forward and backward in terms of these two launches.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Optional
+
+import torch
+from torch import Tensor
+
+from . import kernels, native
+from .functional import _deliver_grad
+from .gemm import EPI_DGELU, EPI_GELU, EPI_PLAIN, gemm_bf16
+
+_MAX = 8
+COPY_CTAS = 16
+#: switched on by ``enable_symmetric_memory`` (off with pipeline parallelism:
+#: a call site's gathered-input buffer is reused by every microbatch in flight)
+ENABLED = False
+#: launches of the two fused kernels by this process (tests assert on it)
+STATS = {"allgather_gemm": 0, "gemm_reduce_scatter": 0}
+
+
+class _FusedComm(ctypes.Structure):
+    _fields_ = [
+        ("ag_src", ctypes.c_void_p * _MAX), ("ag_dst", ctypes.c_void_p), ("ag_ready", ctypes.c_void_p),
+        ("ag_copy_ctas", ctypes.c_int), ("rs_mode", ctypes.c_int),
+        ("rs_stage", ctypes.c_void_p * _MAX), ("rs_out", ctypes.c_void_p * _MAX),
+        ("rs_bias", ctypes.c_void_p), ("rs_residual", ctypes.c_void_p),
+        ("pads", ctypes.c_void_p * _MAX), ("epochs", ctypes.c_void_p), ("counters", ctypes.c_void_p),
+        ("channel", ctypes.c_int), ("rank", ctypes.c_int), ("n_ranks", ctypes.c_int),
+        ("seq_len", ctypes.c_int), ("shard_len", ctypes.c_int), ("rows_per_rank", ctypes.c_int),
+        ("budget", ctypes.c_longlong),
+    ]
+
+
+class TPFused:
+    """Per-TP-group state of the fused kernels: staging buffers, flags, counters."""
+
+    def __init__(self, ws: Any) -> None:
+        from ..distributed.symm_mem import CHANNEL_TP
+
+        self.ws = ws
+        self.channel = CHANNEL_TP
+        assert native.lib().nmb_fused_comm_size() == ctypes.sizeof(_FusedComm), "FusedComm layout mismatch"
+        self.counters = torch.zeros(2, dtype=torch.int32, device=ws.device)
+        self.ready = torch.zeros(4096, dtype=torch.int32, device=ws.device)
+        self._stage: dict[tuple[int, int], list[Tensor]] = {}
+        self._stage_turn: dict[tuple[int, int], int] = {}
+        self._gather: dict[tuple[int, int], Tensor] = {}
+
+    # -- buffers ---------------------------------------------------------------
+    def staging(self, rows: int, cols: int) -> Tensor:
+        """Double-buffered ``[n_ranks, rows/n_ranks, cols]`` staging area (a rank
+        may run one fused op ahead of its peers)."""
+        key = (rows, cols)
+        if key not in self._stage:
+            self._stage[key] = [self.ws.alloc_tensor(rows * cols, torch.bfloat16) for _ in range(2)]
+            self._stage_turn[key] = 0
+        turn = self._stage_turn[key]
+        self._stage_turn[key] = turn ^ 1
+        return self._stage[key][turn]
+
+    def gather_buffer(self, rows: int, cols: int, *, owner: Any = None) -> Tensor:
+        """Symmetric ``[rows, cols]`` buffer for a gathered activation.  With
+        ``owner`` the buffer is private to that call site (it is kept for the
+        backward pass); otherwise one buffer per shape is shared."""
+        key = (rows, cols) if owner is None else (id(owner), rows * cols)
+        buf = self._gather.get(key)
+        if buf is None:
+            buf = self.ws.alloc_tensor(rows * cols, torch.bfloat16).view(rows, cols)
+            self._gather[key] = buf
+        return buf
+
+    def _base(self, seq_len: int, rows: int) -> _FusedComm:
+        ws = self.ws
+        fc = _FusedComm()
+        for i, p in enumerate(ws.pad.peer_ptrs):
+            fc.pads[i] = p
+        fc.epochs = ws.epochs.data_ptr()
+        fc.counters = self.counters.data_ptr()
+        fc.channel = self.channel
+        fc.rank, fc.n_ranks = ws.rank, ws.size
+        fc.seq_len, fc.shard_len = seq_len, seq_len // ws.size
+        fc.rows_per_rank = rows // ws.size
+        fc.budget = ws.budget
+        return fc
+
+    def supported(self, rows: int, seq_len: int, n_out: int) -> bool:
+        t = self.ws.size
+        return (seq_len % t == 0 and (seq_len // t) % 128 == 0 and rows % seq_len == 0 and n_out % 32 == 0
+                and rows // 128 <= self.ready.numel())
+
+    # -- launches ----------------------------------------------------------------
+    def _launch(self, a: Tensor, b: Tensor, b_mn: bool, out: Optional[Tensor], m: int, n: int, k: int,
+                bias: Optional[Tensor], aux_out: Optional[Tensor], mode: int, fc: _FusedComm) -> None:
+        status = native.status_word(a.device)
+        rc = native.lib().nmb_gemm_bf16_fused(
+            native.ptr(a), ctypes.c_int(a.stride(0)), ctypes.c_int(0), native.ptr(b), ctypes.c_int(b.stride(0)),
+            ctypes.c_int(int(b_mn)), native.ptr(out), ctypes.c_int(out.stride(0) if out is not None else n),
+            ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k), native.ptr(bias), native.ptr(aux_out),
+            ctypes.c_int(mode), ctypes.c_float(1.0), ctypes.byref(fc), native.ptr(status),
+            native.stream_ptr(a.device))
+        native.check_rc(rc, "nmb_gemm_bf16_fused")
+        native.launches += 1  # the epoch-advance kernel
+
+    def gemm_reduce_scatter(self, a: Tensor, b: Tensor, seq_len: int, *, b_mn: bool = False,
+                            bias: Optional[Tensor] = None, residual: Optional[Tensor] = None) -> Tensor:
+        """``reduce_scatter_over_sequence(a @ B^T) + bias + residual`` -> ``[rows/t, n]``.
+
+        ``a`` is ``[rows, k]`` with rows ordered ``[batch][sequence]``; logical B
+        is ``[n, k]`` (``b_mn``: stored ``[k, n]``)."""
+        m, k = a.shape
+        n = b.shape[1] if b_mn else b.shape[0]
+        stage = self.staging(m, n)
+        out = torch.empty((m // self.ws.size, n), dtype=torch.bfloat16, device=a.device)
+        fc = self._base(seq_len, m)
+        fc.rs_mode = 1
+        for i, p in enumerate(self.ws.peers_of(stage)):
+            fc.rs_stage[i] = p
+        fc.rs_out[self.ws.rank] = out.data_ptr()
+        fc.rs_bias = bias.data_ptr() if bias is not None else None
+        fc.rs_residual = residual.data_ptr() if residual is not None else None
+        self._launch(a, b, b_mn, None, m, n, k, None, None, EPI_PLAIN, fc)
+        STATS["gemm_reduce_scatter"] += 1
+        return out
+
+    def allgather_gemm(self, full: Tensor, b: Tensor, seq_len: int, *, b_mn: bool = False,
+                       bias: Optional[Tensor] = None, mode: int = EPI_PLAIN,
+                       aux_out: Optional[Tensor] = None) -> Tensor:
+        """``full @ B^T`` where only this rank's sequence shard of the symmetric
+        buffer ``full`` is valid on entry; on return ``full`` holds every shard."""
+        m, k = full.shape
+        n = b.shape[1] if b_mn else b.shape[0]
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=full.device)
+        fc = self._base(seq_len, m)
+        fc.ag_copy_ctas = COPY_CTAS
+        fc.ag_dst = full.data_ptr()
+        fc.ag_ready = self.ready.data_ptr()
+        for i, p in enumerate(self.ws.peers_of(full)):
+            fc.ag_src[i] = p
+        self._launch(full, b, b_mn, out, m, n, k, bias, aux_out, mode, fc)
+        STATS["allgather_gemm"] += 1
+        return out
+
+
+def tp_fused_for(group: Any) -> Optional[TPFused]:
+    from ..distributed import symmetric
+
+    ws = symmetric.workspace_for(group)
+    if ws is None:
+        return None
+    st = getattr(ws, "_tp_fused", None)
+    if st is None:
+        st = TPFused(ws)
+        ws._tp_fused = st
+    return st
+
+
+def _place_shard(full: Tensor, shard: Tensor, rank: int, seq_len: int, size: int) -> None:
+    """Write this rank's ``[B, S/t, K]`` shard into its rows of the ``[B*S, K]`` buffer."""
+    b = full.shape[0] // seq_len
+    width = seq_len // size
+    full.view(b, seq_len, -1)[:, rank * width:(rank + 1) * width].copy_(shard.reshape(b, width, -1))
+
+
+class _SPColumnLinearFn(torch.autograd.Function):
+    """Sequence-parallel column linear: all-gather -> GEMM (+bias, +GELU split)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], st: TPFused, seq_len: int, site: Any,
+                split_gelu: bool):
+        bsz, width, k = x.shape
+        rows = bsz * seq_len
+        full = st.gather_buffer(rows, k, owner=site)
+        _place_shard(full, x, st.ws.rank, seq_len, st.ws.size)
+        n = weight.shape[0]
+        pre = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device) if split_gelu else None
+        y = st.allgather_gemm(full, weight, seq_len, bias=bias, mode=EPI_GELU if split_gelu else EPI_PLAIN,
+                              aux_out=pre)
+        ctx.save_for_backward(full, weight)
+        ctx.meta = (st, seq_len, (weight, bias), x.shape)
+        if split_gelu:
+            y = y.view(bsz, seq_len, n)
+            ctx.mark_non_differentiable(y)
+            return pre.view(bsz, seq_len, n), y
+        return y.view(bsz, seq_len, n)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor, *_unused):
+        full, weight = ctx.saved_tensors
+        st, seq_len, (w_param, b_param), in_shape = ctx.meta
+        n = weight.shape[0]
+        dz = dy.reshape(-1, n)
+        if dz.stride(-1) != 1 or dz.stride(0) % 8 != 0:
+            dz = dz.contiguous()
+        # dgrad partial -> reduce-scatter back to the sequence shard
+        dx = st.gemm_reduce_scatter(dz, weight, seq_len, b_mn=True).view(in_shape)
+        dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dz, full, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        db = None
+        if b_param is not None:
+            db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dz, out=out, accumulate=acc))
+        return dx, dw, db, None, None, None, None
+
+
+class _SPRowLinearFn(torch.autograd.Function):
+    """Sequence-parallel row linear: GEMM -> reduce-scatter (+bias, +residual)."""
+
+    @staticmethod
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor],
+                gelu_pre: Optional[Tensor], st: TPFused, seq_len: int):
+        bsz, s, k = x.shape
+        x2 = x.reshape(-1, k)
+        if x2.stride(-1) != 1 or x2.stride(0) % 8 != 0:
+            x2 = x2.contiguous()
+        n = weight.shape[0]
+        res2 = residual.reshape(-1, n).contiguous() if residual is not None else None
+        out = st.gemm_reduce_scatter(x2, weight, seq_len, bias=bias, residual=res2)
+        pre2 = gelu_pre.reshape(-1, k) if gelu_pre is not None else None
+        ctx.save_for_backward(x2, weight, pre2)
+        ctx.meta = (st, seq_len, (weight, bias), x.shape, residual is not None)
+        return out.view(bsz, seq_len // st.ws.size, n)
+
+    @staticmethod
+    def backward(ctx, dy: Tensor):
+        x2, weight, pre2 = ctx.saved_tensors
+        st, seq_len, (w_param, b_param), in_shape, has_res = ctx.meta
+        n = weight.shape[0]
+        rows = x2.shape[0]
+        # all-gather dY, then dgrad (with GELU' folded in when the input was a GELU)
+        dy_full = st.gather_buffer(rows, n)
+        _place_shard(dy_full, dy, st.ws.rank, seq_len, st.ws.size)
+        if pre2 is not None:
+            # dgrad epilogue needs the pre-activation: plain fused GEMM, then GELU'
+            dact = st.allgather_gemm(dy_full, weight, seq_len, b_mn=True)
+            dx = kernels.gelu_bwd(pre2, dact)
+        else:
+            dx = st.allgather_gemm(dy_full, weight, seq_len, b_mn=True)
+        dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dy_full, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        db = None
+        if b_param is not None:
+            dyl = dy.reshape(-1, n)
+            dyl = dyl if dyl.is_contiguous() else dyl.contiguous()
+            db = kernels.col_sum(dyl)  # partial over this rank's tokens; summed over TP by the SP grad hook
+        d_pre = dx.view(in_shape)
+        if pre2 is not None:
+            return None, dw, db, (dy if has_res else None), d_pre, None, None
+        return d_pre, dw, db, (dy if has_res else None), None, None, None

@@ -318,6 +318,16 @@ class ColumnParallelLinear(nn.Module):
     def forward(self, x: Tensor, *, gelu: bool = False, split_gelu: bool = False):
         """``split_gelu`` returns ``(pre_activation, gelu(pre_activation))`` so that
         the following row-parallel linear can fold GELU' into its dgrad GEMM."""
+        if self.sequence_parallel and self.tp_size > 1 and x.dim() == 3 and OF.native_linear_ok(x, self.weight):
+            from ..ops import fused_tp
+            st = fused_tp.tp_fused_for(self.group) if fused_tp.ENABLED else None
+            seq_len = x.shape[1] * self.tp_size
+            if st is not None and st.supported(x.shape[0] * seq_len, seq_len, self.weight.shape[0]):
+                # all-gather fused into the GEMM (one launch, peers' shards pulled tile by tile)
+                out = fused_tp._SPColumnLinearFn.apply(x, self.weight, self.bias, st, seq_len, self, split_gelu or gelu)
+                if split_gelu:
+                    return out
+                return out[1] if gelu else out
         if self.sequence_parallel:
             x = gather_from_sequence_parallel_region(x, self.group, self.backend, self.tp_rank, self.tp_size)
         elif self.tp_size > 1:
@@ -356,6 +366,13 @@ class RowParallelLinear(nn.Module):
             if fused:
                 return OF.linear_from_gelu(gelu_pre, x, self.weight, self.bias, residual)
             return OF.linear(x, self.weight, self.bias, residual=residual)
+        if self.sequence_parallel and x.dim() == 3 and OF.native_linear_ok(x, self.weight):
+            from ..ops import fused_tp
+            st = fused_tp.tp_fused_for(self.group) if fused_tp.ENABLED else None
+            if st is not None and st.supported(x.shape[0] * x.shape[1], x.shape[1], self.weight.shape[0]):
+                # GEMM with the reduce-scatter (and bias / residual) fused in
+                return fused_tp._SPRowLinearFn.apply(x, self.weight, self.bias, residual,
+                                                     gelu_pre if fused else None, st, x.shape[1])
         out = OF.linear_from_gelu(gelu_pre, x, self.weight, None) if fused else OF.linear(x, self.weight, None)
         if self.sequence_parallel:
             out = reduce_scatter_to_sequence_parallel_region(out, self.group, self.backend, self.tp_rank, self.tp_size)

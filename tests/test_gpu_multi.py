@@ -153,7 +153,10 @@ def worker_tp2_bf16():
 
 
 def worker_sp2_bf16():
+    from nano_megatron_b200.ops import fused_tp
     _gpu_model_worker(GPT2, tensor_parallel_size=2, sequence_parallel=True)
+    # 2 layers: (qkv, fc1) x 2 + lm_head gathers forward, (out, fc2) x 2 gathers backward, and the mirror image
+    assert fused_tp.STATS["allgather_gemm"] >= 9 and fused_tp.STATS["gemm_reduce_scatter"] >= 9, fused_tp.STATS
 
 
 def worker_dp2_bf16():
