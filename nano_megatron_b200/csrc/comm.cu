@@ -175,6 +175,68 @@ allreduce_scale_kernel(PeerPtrs bufs, PeerPtrs pads, uint32_t* epochs, int chann
   if (threadIdx.x == 0) *my_epoch = e0 + 3;
 }
 
+// All-gather through peer stores: every rank writes its `n_vec` 16-byte vectors
+// into slot [rank] of every rank's `[n][n_vec]` destination, then the blocks of
+// equal index meet in a barrier.  Small-message replacement for NCCL
+// all-gather (CE statistics, sequence-parallel replicated-parameter grads,
+// embedding gradients) that can sit inside a captured CUDA graph.
+__global__ void __launch_bounds__(512)
+peer_allgather_kernel(const uint4* __restrict__ src, PeerPtrs dst, PeerPtrs pads, uint32_t* epochs, int channel,
+                      int rank, int n, long long n_vec, int* status, long long budget) {
+  __shared__ uint32_t epoch_s;
+  uint32_t* my_epoch = epochs + channel * kMaxBlocks + blockIdx.x;
+  if (threadIdx.x == 0) epoch_s = *my_epoch;
+  __syncthreads();
+  const uint32_t e0 = epoch_s;
+  const long long per_block = (n_vec + gridDim.x - 1) / gridDim.x;
+  const long long lo = per_block * blockIdx.x;
+  long long hi = lo + per_block;
+  if (hi > n_vec) hi = n_vec;
+  for (int k = 0; k < n; ++k) {
+    uint4* out = static_cast<uint4*>(dst.p[(rank + k) % n]) + static_cast<long long>(rank) * n_vec;
+    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) out[i] = src[i];
+  }
+  block_barrier(pads, channel, rank, n, e0 + 1, status, budget, 66);
+  if (threadIdx.x == 0) *my_epoch = e0 + 1;
+}
+
+// Vocabulary-parallel embedding under sequence parallelism without a
+// reduction: every token's row has exactly one producer (the rank that owns
+// its vocabulary id), which writes token + position embedding straight into
+// the sequence-shard owner's output buffer.
+__global__ void embedding_scatter_kernel(const long long* __restrict__ ids, const long long* __restrict__ positions,
+                                         const __nv_bfloat16* __restrict__ tok, const __nv_bfloat16* __restrict__ pos,
+                                         PeerPtrs out, int n_tokens, int H, int vocab_start, int vloc, int seq_len,
+                                         int shard_len) {
+  const int row = blockIdx.x;
+  if (row >= n_tokens) return;
+  const long long id = ids[row] - vocab_start;
+  if (id < 0 || id >= vloc) return;
+  const int s = row % seq_len;
+  const int owner = s / shard_len;
+  const long long local = static_cast<long long>(row / seq_len) * shard_len + s % shard_len;
+  const uint4* tr = reinterpret_cast<const uint4*>(tok + id * H);
+  const uint4* pr = pos != nullptr ? reinterpret_cast<const uint4*>(pos + positions[row] * H) : nullptr;
+  uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out.p[owner]) + local * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    uint4 v = tr[i];
+    if (pr != nullptr) {
+      const uint4 q = pr[i];
+      const uint32_t a[4] = {v.x, v.y, v.z, v.w};
+      const uint32_t b[4] = {q.x, q.y, q.z, q.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 x = unpack_bf16x2(a[k]);
+        const float2 y = unpack_bf16x2(b[k]);
+        o[k] = pack_bf16x2(x.x + y.x, x.y + y.y);
+      }
+      v = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    dst[i] = v;
+  }
+}
+
 // Stand-alone barrier (one block), e.g. "my buffer is published" between kernels.
 __global__ void barrier_kernel(PeerPtrs pads, uint32_t* epochs, int channel, int rank, int n, int* status,
                                long long budget) {
@@ -255,6 +317,10 @@ extern "C" int nmb_symm_free(void* ptr) {
   return e == cudaSuccess ? 0 : 400 + e;
 }
 
+static void fill(PeerPtrs& t, void* const* src, int n) {
+  for (int i = 0; i < kMaxRanks; ++i) t.p[i] = i < n ? src[i] : nullptr;
+}
+
 extern "C" int nmb_comm_limits(int* max_ranks, int* max_blocks, int* channels) {
   *max_ranks = kMaxRanks;
   *max_blocks = kMaxBlocks;
@@ -262,9 +328,6 @@ extern "C" int nmb_comm_limits(int* max_ranks, int* max_blocks, int* channels) {
   return 0;
 }
 
-static void fill(PeerPtrs& t, void* const* src, int n) {
-  for (int i = 0; i < kMaxRanks; ++i) t.p[i] = i < n ? src[i] : nullptr;
-}
 
 // bufs[n], pads[n]: per-rank device pointers (peer-mapped); numel elements of
 // bf16 (is_bf16) or fp32.  numel * elem_size must be a multiple of 16.
@@ -286,6 +349,39 @@ extern "C" int nmb_allreduce_scale(void* const* bufs, void* const* pads, void* e
   else
     allreduce_scale_kernel<float><<<blocks, 512, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
                                                          numel / per, scale, status, budget_cycles);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+// src: numel*elem bytes (multiple of 16); dsts[n]: every rank's [n][same bytes] buffer.
+extern "C" int nmb_peer_allgather(const void* src, void* const* dsts, void* const* pads, void* epochs, int channel,
+                                  int rank, int n, long long nbytes, int* status, long long budget_cycles,
+                                  void* stream) {
+  if (n < 1 || n > kMaxRanks || channel < 0 || channel >= kChannels || nbytes % 16 != 0) return kBadArgument;
+  PeerPtrs d, p;
+  fill(d, dsts, n);
+  fill(p, pads, n);
+  const long long n_vec = nbytes / 16;
+  int blocks = static_cast<int>((n_vec + 4095) / 4096);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 64) blocks = 64;
+  peer_allgather_kernel<<<blocks, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), d, p, static_cast<uint32_t*>(epochs), channel, rank, n, n_vec, status,
+      budget_cycles);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+extern "C" int nmb_embedding_scatter(const long long* ids, const long long* positions, const void* tok,
+                                     const void* pos, void* const* outs, int n_ranks, int n_tokens, int H,
+                                     int vocab_start, int vloc, int seq_len, int shard_len, void* stream) {
+  if (n_tokens <= 0) return 0;
+  if (H % 8 != 0 || n_ranks < 1 || n_ranks > kMaxRanks) return kBadArgument;
+  PeerPtrs o;
+  fill(o, outs, n_ranks);
+  embedding_scatter_kernel<<<n_tokens, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, positions, static_cast<const __nv_bfloat16*>(tok), static_cast<const __nv_bfloat16*>(pos), o, n_tokens, H,
+      vocab_start, vloc, seq_len, shard_len);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + e;
 }

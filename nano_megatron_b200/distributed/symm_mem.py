@@ -143,6 +143,42 @@ class SymmetricWorkspace:
             native.ptr(self.status), ctypes.c_longlong(self.budget), native.stream_ptr(self.device))
         native.check_rc(rc, "nmb_allreduce_scale")
 
+    def all_gather(self, src: torch.Tensor, *, channel: int = CHANNEL_AUX) -> torch.Tensor:
+        """``[size, *src.shape]`` with every rank's ``src`` (peer stores + one flag
+        round; a plain kernel, so it can be captured in a CUDA graph).  The result
+        lives in a cached symmetric buffer that is overwritten by the second next
+        call with the same shape: consume it (or copy it) before that."""
+        src = src.contiguous()
+        nbytes = src.numel() * src.element_size()
+        if nbytes % 16 != 0:
+            raise ValueError("peer all-gather needs a multiple of 16 bytes")
+        key = (nbytes, src.dtype)
+        cache = self.__dict__.setdefault("_ag_cache", {})
+        if key not in cache:
+            cache[key] = [[self.alloc_tensor(self.size * src.numel(), src.dtype) for _ in range(2)], 0]
+        bufs, turn = cache[key]
+        cache[key][1] = turn ^ 1
+        dst = bufs[turn]
+        rc = native.lib().nmb_peer_allgather(
+            native.ptr(src), self.peer_table(dst), self.pad.table(), native.ptr(self.epochs), ctypes.c_int(channel),
+            ctypes.c_int(self.rank), ctypes.c_int(self.size), ctypes.c_longlong(nbytes), native.ptr(self.status),
+            ctypes.c_longlong(self.budget), native.stream_ptr(self.device))
+        native.check_rc(rc, "nmb_peer_allgather")
+        return dst.view(self.size, *src.shape)
+
+    def embedding_scatter(self, ids: torch.Tensor, positions: Optional[torch.Tensor], tok_w: torch.Tensor,
+                          pos_w: Optional[torch.Tensor], out: torch.Tensor, vocab_start: int, seq_len: int) -> None:
+        """Every token row owned by this rank's vocabulary shard is written (token +
+        position embedding) into the sequence-shard owner's ``out`` (symmetric,
+        ``[B * S/size, H]``)."""
+        n_tokens = ids.numel()
+        rc = native.lib().nmb_embedding_scatter(
+            native.ptr(ids), native.ptr(positions), native.ptr(tok_w), native.ptr(pos_w), self.peer_table(out),
+            ctypes.c_int(self.size), ctypes.c_int(n_tokens), ctypes.c_int(tok_w.shape[1]), ctypes.c_int(vocab_start),
+            ctypes.c_int(tok_w.shape[0]), ctypes.c_int(seq_len), ctypes.c_int(seq_len // self.size),
+            native.stream_ptr(self.device))
+        native.check_rc(rc, "nmb_embedding_scatter")
+
     def make_allreduce_mean(self, flat: torch.Tensor) -> Callable[[torch.Tensor, int], bool]:
         """Reducer for a DDP bucket whose buffer is ``flat`` (see ``GradBucket.fused_reduce``)."""
         per = 8 if flat.dtype == torch.bfloat16 else 4

@@ -108,3 +108,76 @@ class _CPFlashPeer(torch.autograd.Function):
 def cp_flash_attention_peer(q: Tensor, k: Tensor, v: Tensor, scale: float, ws: SymmetricWorkspace, cp_rank: int,
                             cp_size: int) -> Tensor:
     return _CPFlashPeer.apply(q, k.contiguous(), v.contiguous(), float(scale), ws, cp_rank, cp_size)
+
+
+class _SPEmbeddingFn(torch.autograd.Function):
+    """Vocabulary-parallel embedding whose output is sequence-sharded.
+
+    The reference all-reduces the masked lookups of all ranks and then narrows
+    to the local sequence shard (nano_megatron/model/tp_gpt.py:546-561).  Each
+    row has exactly one non-zero contributor, so no arithmetic is needed: the
+    rank that owns a token's vocabulary id writes the row (token + position
+    embedding) directly into the buffer of the rank that owns its sequence
+    position.  Backward gathers the gradient shards and scatter-adds the rows of
+    this rank's vocabulary shard.
+    """
+
+    @staticmethod
+    def forward(ctx: Any, ids: Tensor, positions, tok_w: Tensor, pos_w, vocab_start: int, ws: SymmetricWorkspace,
+                site: Any):
+        b, s = ids.shape
+        h = tok_w.shape[1]
+        rows = b * s // ws.size
+        cache = ws.__dict__.setdefault("_emb_out", {})
+        key = (id(site), rows, h)
+        if key not in cache:
+            cache[key] = ws.alloc_tensor(rows * h, tok_w.dtype).view(rows, h)
+        out = cache[key]
+        ids_c = ids.contiguous()
+        pos_c = positions.contiguous() if positions is not None else None
+        ws.barrier()                      # every rank is done with the previous step's output
+        ws.embedding_scatter(ids_c, pos_c, tok_w, pos_w, out, vocab_start, s)
+        ws.barrier()                      # every row of my shard has been written
+        ctx.save_for_backward(ids_c, pos_c)
+        ctx.meta = (tok_w, pos_w, vocab_start, ws, (b, s, h))
+        return out.view(b, s // ws.size, h).clone()
+
+    @staticmethod
+    def backward(ctx: Any, dy: Tensor):
+        from ..ops import kernels
+
+        ids, positions = ctx.saved_tensors
+        tok_w, pos_w, vocab_start, ws, (b, s, h) = ctx.meta
+        width = s // ws.size
+        shards = ws.all_gather(dy.contiguous())                       # [ranks, B, S/t, H]
+        full = shards.permute(1, 0, 2, 3).reshape(b, s, h).contiguous()
+        results = []
+        for param in (tok_w, pos_w):
+            if param is None:
+                results.append((None, None))
+                continue
+            # sequence-parallel replicated parameters must go through autograd so that
+            # their TP gradient hook runs
+            main = None if getattr(param, "_nmb_sp_replicated", False) else getattr(param, "main_grad", None)
+            results.append((main if main is not None else torch.zeros_like(param), main is not None))
+        d_tok, tok_direct = results[0]
+        d_pos, pos_direct = results[1]
+        kernels.embedding_bwd(ids, None, full, d_tok, None, vocab_start)
+        if d_pos is not None:
+            # Position rows: only this rank's sequence shard, i.e. a partial sum that
+            # the sequence-parallel gradient hook completes over the TP group.
+            lo = ws.rank * width
+            kernels.embedding_bwd(ids[:, lo:lo + width].contiguous(), positions[:, lo:lo + width].contiguous(),
+                                  dy.contiguous(), None, d_pos, vocab_start)
+        for param, direct in ((tok_w, tok_direct), (pos_w, pos_direct)):
+            if param is not None and direct:
+                ready = getattr(param, "_nmb_grad_ready", None)
+                if ready is not None:
+                    ready()
+        return (None, None, None if tok_direct else d_tok, None if (pos_w is None or pos_direct) else d_pos,
+                None, None, None)
+
+
+def sp_embedding(ids: Tensor, positions, tok_w: Tensor, pos_w, vocab_start: int, ws: SymmetricWorkspace,
+                 site: Any) -> Tensor:
+    return _SPEmbeddingFn.apply(ids, positions, tok_w, pos_w, vocab_start, ws, site)

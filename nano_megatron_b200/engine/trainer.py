@@ -59,12 +59,21 @@ class Trainer:
         ctx = self.ctx
         if getattr(ctx, "world_size", 1) == 1:
             return True
-        if ctx.tensor_parallel_size > 1 or ctx.pipeline_parallel_size > 1:
+        if ctx.pipeline_parallel_size > 1:
             return False
+        if ctx.tensor_parallel_size > 1:
+            # sequence-parallel TP with every collective on peer-memory kernels
+            from ..distributed import symmetric
+            from ..ops import fused_tp
+            if not (ctx.sequence_parallel and fused_tp.ENABLED
+                    and symmetric.workspace_for(ctx.tensor_parallel_group) is not None):
+                return False
         if ctx.context_parallel_size > 1:
             from ..distributed import symmetric
             if symmetric.workspace_for(ctx.context_parallel_group) is None:
                 return False
+        if ctx.data_parallel_size * ctx.context_parallel_size == 1:
+            return True                     # no gradient reduction at all
         return all(b.fused_reduce is not None for b in self.ddp._buckets)
 
     # ------------------------------------------------------------------ step --

@@ -335,6 +335,15 @@ class TPGPT(nn.Module):
         if self._cp_size > 1:
             start, end = local_sequence_range(self._cp_rank, self._cp_size, seq_len)
             input_ids, positions = input_ids[:, start:end], positions[:, start:end]
+        if self._sequence_parallel and self._tp_size > 1 and OF.use_native(self.tok_emb.weight):
+            from ..distributed import symmetric
+            ws = symmetric.workspace_for(self._tp_group)
+            if ws is not None and self.tok_emb.weight.shape[1] % 8 == 0:
+                from ..distributed.symm_ops import sp_embedding
+                width = seq_len // self._tp_size
+                x = sp_embedding(input_ids, positions if pos_w is not None else None, self.tok_emb.weight, pos_w,
+                                 self.vocab_start_index, ws, self)
+                return x, positions[:, self._tp_rank * width:(self._tp_rank + 1) * width]
         if self._sequence_parallel and self._tp_size > 1:
             partial = OF.embedding(input_ids, None, self.tok_emb.weight, None, self.vocab_start_index)
             x = reduce_scatter_to_sequence_parallel_region(partial, self._tp_group, self._tp_backend, self._tp_rank,

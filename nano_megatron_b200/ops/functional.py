@@ -37,6 +37,8 @@ def _deliver_grad(param: Optional[Tensor], compute, *, shape_like: Optional[Tens
     """Run ``compute(out, accumulate)``; returns the grad for autograd or None
     when it was accumulated into ``param.main_grad``."""
     main = getattr(param, "main_grad", None) if param is not None else None
+    if main is not None and getattr(param, "_nmb_sp_replicated", False):
+        main = None  # its TP gradient hook only runs on the autograd path
     if main is not None:
         compute(main, True)
         ready = getattr(param, "_nmb_grad_ready", None)
@@ -356,8 +358,13 @@ class _CrossEntropyFn(torch.autograd.Function):
         target = target.contiguous()
         stats = kernels.ce_stats(logits, target, vocab_start)
         if tp_size > 1:
-            gathered = torch.empty((tp_size, *stats.shape), dtype=stats.dtype, device=stats.device)
-            backend.all_gather_into_tensor(gathered.view(-1, stats.shape[-1]), stats, group=group)
+            from ..distributed import symmetric
+            ws = symmetric.workspace_for(group)
+            if ws is not None and (stats.numel() * 4) % 16 == 0:
+                gathered = ws.all_gather(stats)             # peer stores, graph-capturable
+            else:
+                gathered = torch.empty((tp_size, *stats.shape), dtype=stats.dtype, device=stats.device)
+                backend.all_gather_into_tensor(gathered.view(-1, stats.shape[-1]), stats, group=group)
         else:
             gathered = stats.unsqueeze(0)
         lse, accum, _ = kernels.ce_combine(gathered, target, ignore_index)

@@ -195,8 +195,18 @@ class _SPGradReducer:
             by_dtype.setdefault(item[1].dtype, []).append(item)
         for items in by_dtype.values():
             local = torch.cat([g.reshape(-1) for _, g in items])
-            total = local.clone()
-            _wait(self.backend.all_reduce(total, group=self.group, op="sum", async_op=True))
+            ws = None
+            if local.is_cuda:
+                from ..distributed import symmetric
+                ws = symmetric.workspace_for(self.group)
+            if ws is not None:
+                pad = (-local.numel()) % 8
+                padded = torch.nn.functional.pad(local, (0, pad)) if pad else local
+                everyone = ws.all_gather(padded)            # [ranks, n]; peer stores, no NCCL
+                total = everyone.float().sum(0)[: local.numel()].to(local.dtype)
+            else:
+                total = local.clone()
+                _wait(self.backend.all_reduce(total, group=self.group, op="sum", async_op=True))
             remote = total - local
             offset = 0
             for p, g in items:
