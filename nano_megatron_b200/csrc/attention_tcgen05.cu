@@ -388,7 +388,7 @@ struct AttnBwdParams {
   long long dkv_stride_b, dkv_stride_s, dkv_stride_h;
   const float* lse;    // [B, Hq, Sq]
   const float* delta;  // [B, Hq, Sq]  rowsum(dO * O)
-  float* dq_acc;       // [B, Sq, Hq, d] fp32, zero-initialised
+  float* dq_acc;       // [B, Hq, Sq, d] fp32 (chunk-swizzled rows), zero-initialised
   int B, Hq, Hkv, Sq;
   int chunk_len, n_chunks;
   int d;
@@ -408,12 +408,12 @@ struct AttnBwdSmem {
   static constexpr int kDO = kQ + kQStages * kTile;
   static constexpr int kP = kDO + kQStages * kTile;
   static constexpr int kDS = kP + 32768;
-  // fp32 staging of the dQ tile for the bulk reduce-add.  HD == 64: its own
-  // buffer with rows padded by 16 B (no bank conflicts); HD == 128: aliases the
-  // P + dS buffers (64 KiB, unpadded rows).
+  // fp32 staging of the dQ tile for the bulk reduce-add (128 rows x d floats,
+  // 16-byte chunks XOR-swizzled by the row so that row-per-thread writes are
+  // conflict free).  HD == 64: its own buffer; HD == 128: aliases P + dS.
   static constexpr bool kStageAlias = HD > 64;
   static constexpr int kStage = kStageAlias ? kP : kDS + 32768;
-  static constexpr int kStageBytes = kStageAlias ? 0 : 128 * (HD + 4) * 4;
+  static constexpr int kStageBytes = kStageAlias ? 0 : 128 * HD * 4;
   static constexpr int kBar = kDS + 32768 + kStageBytes;
   static constexpr int kNumBars = 1 + 2 * kQStages + 4;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
@@ -585,21 +585,22 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       if (!valid) limit = -1;
       // CTA-uniform: every (query, key) pair of this tile is visible and valid.
       const bool tile_full = (kv0 + 127 <= p.q_pos0 + q0) && (q0 + 127 < p.Sq) && (kv0 + 128 <= skv_total);
-      if (!mbar_wait(sdp_full, i & 1, abort_flag, p.status, 48)) {
-        ok = false;
-        break;
-      }
+      // A failed wait must not leave the other threads stuck in a named
+      // barrier: a thread that gave up keeps walking the loop and executes the
+      // barriers only (`ok` is kept warp-uniform for the .sync.aligned TMEM ops).
+      if (ok && !mbar_wait(sdp_full, i & 1, abort_flag, p.status, 48)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
       if (L::kStageAlias && i > 0) {
-        // The dQ staging rows alias P / dS: every thread's bulk reduce must have
-        // finished reading before anyone overwrites them.
-        bulk_wait_read();
+        // The dQ staging tile aliases P / dS: the bulk reduce must have finished
+        // reading it before anyone overwrites it.
+        if (r == 0) bulk_wait_read();
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
       uint8_t* sp = smem + L::kP;
       uint8_t* sds = smem + L::kDS;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < (ok ? 4 : 0); ++c) {
         uint32_t sr[32], dpr[32];
         tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
         tmem_ld_32x32(t_lane + kDPCol + c * 32, dpr);
@@ -637,37 +638,45 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(pds_full);
-      if (!mbar_wait(dq_full, i & 1, abort_flag, p.status, 49)) {
-        ok = false;
-        break;
-      }
+      if (ok) mbar_arrive(pds_full);
+      if (ok && !mbar_wait(dq_full, i & 1, abort_flag, p.status, 49)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
-      // dQ tile: TMEM -> fp32 staging row of this thread -> one bulk reduce-add
-      // per row into the global accumulator (replaces 64..128 scalar atomics).
-      const int pitch = L::kStageAlias ? p.d : HD + 4;  // floats
-      float* stage_row = reinterpret_cast<float*>(smem + L::kStage) + r * pitch;
-      if (!L::kStageAlias) bulk_wait_read();  // my previous reduce has read its row
+      // dQ tile: TMEM -> fp32 staging tile (swizzled) -> ONE bulk reduce-add of
+      // the whole tile into the global accumulator, whose tiles use the same
+      // swizzled element order (attn_dq_store_kernel undoes it).
+      float* stage = reinterpret_cast<float*>(smem + L::kStage);
+      if (!L::kStageAlias) {
+        if (r == 0) bulk_wait_read();  // the previous tile's reduce has read the buffer
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      float* stage_row = stage + r * p.d;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < (ok ? HD / 32 : 0); ++c) {
         uint32_t qr[32];
         tmem_ld_32x32(t_lane + kDQCol + c * 32, qr);
         tmem_ld_wait();
         if (c * 32 < p.d) {
 #pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4)
-            *reinterpret_cast<uint4*>(stage_row + c * 32 + q4 * 4) =
+          for (int q4 = 0; q4 < 8; ++q4) {
+            const int chunk = c * 8 + q4;                                   // 16-byte chunk of the row
+            const int phys = (chunk & ~7) | ((chunk ^ r) & 7);              // XOR swizzle inside 128-byte groups
+            *reinterpret_cast<uint4*>(stage_row + phys * 4) =
                 make_uint4(qr[q4 * 4], qr[q4 * 4 + 1], qr[q4 * 4 + 2], qr[q4 * 4 + 3]);
+          }
         }
       }
       tc_fence_before();
-      mbar_arrive(dq_empty);
+      if (ok) mbar_arrive(dq_empty);
       fence_proxy_async_smem();
-      if (valid) {
-        float* dq_row = p.dq_acc + ((static_cast<long long>(b) * p.Sq + q_row) * p.Hq + hq) * p.d;
-        bulk_reduce_add_f32(dq_row, stage_row, p.d * 4);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (r == 0 && ok) {
+        int rows_valid = p.Sq - q0;
+        if (rows_valid > 128) rows_valid = 128;
+        float* dq_tile = p.dq_acc + ((static_cast<long long>(b) * p.Hq + hq) * p.Sq + q0) * p.d;
+        bulk_reduce_add_f32(dq_tile, stage, static_cast<uint32_t>(rows_valid) * p.d * 4);
+        bulk_commit();
       }
-      bulk_commit();
     }
     bulk_wait_all();
     // dK / dV of this tile: the last dq_full also covers their MMAs.
@@ -765,28 +774,32 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const 
   }
 }
 
-// dq (bf16, strided) <- dq_acc (fp32, [B, S, H, d]); 8 elements per thread.
+// dq (bf16, strided) <- dq_acc (fp32, [B, H, S, d] with the 16-byte chunks of a
+// row XOR-swizzled by (s % 128) & 7 inside each group of eight); 8 elements per thread.
 __global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dq,
                                      long long dq_sb, long long dq_ss, long long dq_sh, int B, int H,
                                      int S, int d) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long total = static_cast<long long>(B) * S * H * d / 8;
   if (idx >= total) return;
-  const long long e = idx * 8;
-  const int c = e % d;
-  const long long row = e / d;
-  const int h = row % H;
-  const long long bs = row / H;
-  const int s = bs % S;
-  const int b = bs / S;
-  const float4 v0 = reinterpret_cast<const float4*>(dq_acc + e)[0];
-  const float4 v1 = reinterpret_cast<const float4*>(dq_acc + e)[1];
+  const int per_row = d / 8;
+  const int c8 = static_cast<int>(idx % per_row);   // which 8 columns of the row
+  const long long row = idx / per_row;              // (b * H + h) * S + s
+  const int s = row % S;
+  const long long bh = row / S;
+  const int h = bh % H;
+  const int b = bh / H;
+  const int r = s & 127;
+  const float* src = dq_acc + row * d;
+  const int c0 = 2 * c8, c1 = 2 * c8 + 1;           // the two 16-byte chunks
+  const float4 v0 = *reinterpret_cast<const float4*>(src + ((c0 & ~7) | ((c0 ^ r) & 7)) * 4);
+  const float4 v1 = *reinterpret_cast<const float4*>(src + ((c1 & ~7) | ((c1 ^ r) & 7)) * 4);
   uint4 out;
   out.x = pack_bf16x2(v0.x, v0.y);
   out.y = pack_bf16x2(v0.z, v0.w);
   out.z = pack_bf16x2(v1.x, v1.y);
   out.w = pack_bf16x2(v1.z, v1.w);
-  *reinterpret_cast<uint4*>(dq + b * dq_sb + s * dq_ss + h * dq_sh + c) = out;
+  *reinterpret_cast<uint4*>(dq + b * dq_sb + s * dq_ss + h * dq_sh + c8 * 8) = out;
 }
 
 static int make_attn_map(CUtensorMap* m, const void* ptr, int d, int S, int H, int B, long long ss,
