@@ -395,7 +395,22 @@ struct AttnBwdParams {
   int q_pos0;
   float scale;
   int* status;
+#ifdef NMB_ATTN_PROF
+  long long* prof;  // [8] cycle counters of CTA (0,0,0), thread 0 (profiling builds only)
+#endif
 };
+
+#ifdef NMB_ATTN_PROF
+#define NMB_PROF_DECL long long pt0 = 0, pacc[6] = {0, 0, 0, 0, 0, 0}; const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+#define NMB_PROF_START() do { if (prof_on) pt0 = clock64(); } while (0)
+#define NMB_PROF_LAP(k) do { if (prof_on) { const long long t = clock64(); pacc[k] += t - pt0; pt0 = t; } } while (0)
+#define NMB_PROF_STORE() do { if (prof_on) { for (int k = 0; k < 6; ++k) p.prof[k] = pacc[k]; p.prof[6] = n_iter; } } while (0)
+#else
+#define NMB_PROF_DECL
+#define NMB_PROF_START()
+#define NMB_PROF_LAP(k)
+#define NMB_PROF_STORE()
+#endif
 
 template <int HD>
 struct AttnBwdSmem {
@@ -415,12 +430,15 @@ struct AttnBwdSmem {
   static constexpr int kStage = kStageAlias ? kP : kDS + 32768;
   static constexpr int kStageBytes = kStageAlias ? 0 : 128 * HD * 4;
   static constexpr int kBar = kDS + 32768 + kStageBytes;
-  static constexpr int kNumBars = 1 + 2 * kQStages + 4;
+  static constexpr int kNumBars = 1 + 2 * kQStages + 8;
   static constexpr int kTotal = kBar + kNumBars * 8 + 16;
 };
 
+constexpr int kBwdThreads = 320;       // 8 compute warps, TMA warp, MMA warp
+constexpr int kBwdCompute = 256;
+
 template <int HD>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   using L = AttnBwdSmem<HD>;
   constexpr int NS = L::kSlabs;
@@ -432,9 +450,11 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   uint64_t* q_full = &bars[1];          // [QS]
   uint64_t* q_empty = &bars[1 + QS];    // [QS]
   uint64_t* sdp_full = &bars[1 + 2 * QS];
-  uint64_t* pds_full = sdp_full + 1;
-  uint64_t* dq_full = sdp_full + 2;
-  uint64_t* dq_empty = sdp_full + 3;
+  uint64_t* pds_full = sdp_full + 1;    // P / dS written to shared memory (256 arrivals)
+  uint64_t* dq_full = sdp_full + 2;     // [2] dQ MMAs of tile j done: barrier j & 1, phase j >> 1
+  uint64_t* dq_empty = sdp_full + 4;    // [2] dQ of tile j read out of TMEM (256 arrivals)
+  uint64_t* pds_free = sdp_full + 6;    // dV / dK (and dQ) MMAs done: P / dS / Q / dO stage reusable
+  uint64_t* sdp_read = sdp_full + 7;    // S / dP copied to registers (256 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(&bars[L::kNumBars]);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -455,7 +475,9 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   const int n_iter = per_head * group;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kSCol = 0, kDPCol = 128, kDVCol = 256, kDKCol = 256 + HD;
+  // HD == 64 leaves room for two dQ accumulators (tile j uses j & 1)
   constexpr uint32_t kDQCol = kAliasDQ ? 0 : 256 + 2 * HD;
+  constexpr uint32_t kDQStep = kAliasDQ ? 0 : HD;
 
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) report_status(p.status, kBadArgument, 40);
@@ -468,13 +490,17 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       mbar_init(&q_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 128);
-    mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 128);
+    mbar_init(pds_full, kBwdCompute);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&dq_full[s], 1);
+      mbar_init(&dq_empty[s], kBwdCompute);
+    }
+    mbar_init(pds_free, 1);
+    mbar_init(sdp_read, kBwdCompute);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -483,7 +509,8 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
+    // ------------------------------------------------------------ producer --
     if (lane == 0 && n_iter > 0) {
       mbar_expect_tx(kv_full, 2 * L::kTile);
 #pragma unroll
@@ -505,7 +532,8 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
+    // ---------------------------------------------------------- MMA issuer --
     if (lane == 0 && n_iter > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S, dP
       constexpr uint32_t idesc_kv = make_idesc_bf16(128, HD, true, true);     // dV, dK
@@ -538,11 +566,26 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         issue_sdp(0);
       }
       for (int i = 0; i < n_iter && ok; ++i) {
+        if (!kAliasDQ && i + 1 < n_iter) {
+          // S / dP live in registers once read: the next tile's scores are
+          // computed while the compute warps are still busy with this tile.
+          if (!mbar_wait(sdp_read, i & 1, abort_flag, p.status, 53)) break;
+          if (!mbar_wait(&q_full[(i + 1) % QS], ((i + 1) / QS) & 1, abort_flag, p.status, 46)) break;
+          tc_fence_after();
+          issue_sdp(i + 1);
+        }
         if (!mbar_wait(pds_full, i & 1, abort_flag, p.status, 44)) break;
-        if (!kAliasDQ && i > 0 && !mbar_wait(dq_empty, (i - 1) & 1, abort_flag, p.status, 45)) break;
+        if (!kAliasDQ && i > 1 && !mbar_wait(&dq_empty[i & 1], ((i - 2) >> 1) & 1, abort_flag, p.status, 45)) break;
         tc_fence_after();
         const uint32_t sQ = smem_u32(smem + L::kQ + (i % QS) * L::kTile);
         const uint32_t sDO = smem_u32(smem + L::kDO + (i % QS) * L::kTile);
+        // dQ first: the compute warps stream it out while dV / dK accumulate.
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dQ = dS K
+          tc_mma_bf16(tmem_base + kDQCol + (i & 1) * kDQStep,
+                      make_smem_desc(sDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                      make_smem_desc(sK + k * 2048, 16384, 1024), idesc_dq, k != 0 ? 1u : 0u);
+        tc_commit(&dq_full[i & 1]);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // dV += P^T dO
           tc_mma_bf16(tmem_base + kDVCol, make_smem_desc(sP + k * 2048, 16384, 1024),
@@ -551,27 +594,86 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
         for (int k = 0; k < 8; ++k)  // dK += dS^T Q
           tc_mma_bf16(tmem_base + kDKCol, make_smem_desc(sDS + k * 2048, 16384, 1024),
                       make_smem_desc(sQ + k * 2048, 16384, 1024), idesc_kv, (i | k) != 0 ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 8; ++k)  // dQ = dS K
-          tc_mma_bf16(tmem_base + kDQCol,
-                      make_smem_desc(sDS + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
-                      make_smem_desc(sK + k * 2048, 16384, 1024), idesc_dq, k != 0 ? 1u : 0u);
-        tc_commit(dq_full);
+        tc_commit(pds_free);
         tc_commit(&q_empty[i % QS]);
-        if (i + 1 < n_iter) {
+        if (kAliasDQ && i + 1 < n_iter) {
           const int st = (i + 1) % QS;
           if (!mbar_wait(&q_full[st], ((i + 1) / QS) & 1, abort_flag, p.status, 46)) break;
-          if (kAliasDQ && !mbar_wait(dq_empty, i & 1, abort_flag, p.status, 47)) break;
+          if (!mbar_wait(&dq_empty[i & 1], (i >> 1) & 1, abort_flag, p.status, 47)) break;
           tc_fence_after();
           issue_sdp(i + 1);
         }
       }
     }
   } else {
-    const int r = threadIdx.x;
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    // ------------------------------------------------------------- compute --
+    // Two threads per query row: warps w and w + 4 share a TMEM lane quadrant
+    // and each takes one half of the columns.
+    const int quad = warp & 3;
+    const int half = warp >> 2;
+    const int r = quad * 32 + lane;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
     const float sl2 = p.scale * kLog2e;
+    float* stage = reinterpret_cast<float*>(smem + L::kStage);
+    float* stage_row = stage + r * p.d;
     bool ok = true;
+    NMB_PROF_DECL
+
+    // dQ of tile j: TMEM -> fp32 staging tile (swizzled) -> ONE bulk reduce-add
+    // of the whole tile into the global accumulator, whose tiles use the same
+    // swizzled element order (attn_dq_store_kernel undoes it).  A failed wait
+    // must not leave the other threads stuck in a named barrier: a thread that
+    // gave up executes the barriers only (`ok` is kept warp-uniform for the
+    // .sync.aligned TMEM instructions).
+    auto dq_out = [&](int j) {
+      if (ok && !mbar_wait(&dq_full[j & 1], (j >> 1) & 1, abort_flag, p.status, 49)) ok = false;
+      // aliased staging: the dV / dK MMAs read P / dS until pds_free
+      if (L::kStageAlias && ok && !mbar_wait(pds_free, j & 1, abort_flag, p.status, 51)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+      NMB_PROF_LAP(3);  // waited for the dQ MMAs
+      if (!L::kStageAlias) {
+        if (threadIdx.x == 0) bulk_wait_read();  // the previous tile's reduce has read the buffer
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+      }
+      constexpr int kDqChunks = HD / 64;  // 32-column chunks per thread
+      if (ok) {
+        uint32_t qr[kDqChunks][32];
+#pragma unroll
+        for (int cc = 0; cc < kDqChunks; ++cc)
+          tmem_ld_32x32(t_lane + kDQCol + (j & 1) * kDQStep + (half * kDqChunks + cc) * 32, qr[cc]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&dq_empty[j & 1]);
+#pragma unroll
+        for (int cc = 0; cc < kDqChunks; ++cc) {
+          const int c = half * kDqChunks + cc;
+          if (c * 32 < p.d) {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              const int ch = c * 8 + q4;                                  // 16-byte chunk of the row
+              const int phys = (ch & ~7) | ((ch ^ r) & 7);                // XOR swizzle inside 128-byte groups
+              *reinterpret_cast<uint4*>(stage_row + phys * 4) =
+                  make_uint4(qr[cc][q4 * 4], qr[cc][q4 * 4 + 1], qr[cc][q4 * 4 + 2], qr[cc][q4 * 4 + 3]);
+            }
+          }
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (threadIdx.x == 0 && ok) {
+        const int hq = hk * group + j / per_head;
+        const int q0 = (qt_first + j % per_head) * 128;
+        int rows_valid = p.Sq - q0;
+        if (rows_valid > 128) rows_valid = 128;
+        float* dq_tile = p.dq_acc + ((static_cast<long long>(b) * p.Hq + hq) * p.Sq + q0) * p.d;
+        bulk_reduce_add_f32(dq_tile, stage, static_cast<uint32_t>(rows_valid) * p.d * 4);
+        bulk_commit();
+      }
+      NMB_PROF_LAP(4);  // dQ write-out
+    };
+
+    NMB_PROF_START();
     for (int i = 0; i < n_iter; ++i) {
       const int hq = hk * group + i / per_head;
       const int q0 = (qt_first + i % per_head) * 128;
@@ -585,124 +687,116 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
       if (!valid) limit = -1;
       // CTA-uniform: every (query, key) pair of this tile is visible and valid.
       const bool tile_full = (kv0 + 127 <= p.q_pos0 + q0) && (q0 + 127 < p.Sq) && (kv0 + 128 <= skv_total);
-      // A failed wait must not leave the other threads stuck in a named
-      // barrier: a thread that gave up keeps walking the loop and executes the
-      // barriers only (`ok` is kept warp-uniform for the .sync.aligned TMEM ops).
       if (ok && !mbar_wait(sdp_full, i & 1, abort_flag, p.status, 48)) ok = false;
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
+      NMB_PROF_LAP(0);  // waited for S / dP
+      // this thread's 64 columns of P and dS, packed to bf16 pairs
+      uint32_t pp[2][16], dd[2][16];
+      if (ok) {
+        uint32_t sr[2][32], dpr[2][32];  // all four TMEM loads in flight at once
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          tmem_ld_32x32(t_lane + kSCol + (half * 2 + cc) * 32, sr[cc]);
+          tmem_ld_32x32(t_lane + kDPCol + (half * 2 + cc) * 32, dpr[cc]);
+        }
+        tmem_ld_wait();
+        if (!kAliasDQ) {
+          tc_fence_before();
+          mbar_arrive(sdp_read);
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 2 + cc;
+          if (tile_full) {
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[cc][jj]), sl2, -lse2));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[cc][jj + 1]), sl2, -lse2));
+              const float d0 = p0 * fmaf(__uint_as_float(dpr[cc][jj]), p.scale, -dlt_s);
+              const float d1 = p1 * fmaf(__uint_as_float(dpr[cc][jj + 1]), p.scale, -dlt_s);
+              pp[cc][jj / 2] = pack_bf16x2(p0, p1);
+              dd[cc][jj / 2] = pack_bf16x2(d0, d1);
+            }
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; jj += 2) {
+              const bool v0 = c * 32 + jj <= limit;
+              const bool v1 = c * 32 + jj + 1 <= limit;
+              const float p0 = v0 ? fast_exp2(fmaf(__uint_as_float(sr[cc][jj]), sl2, -lse2)) : 0.f;
+              const float p1 = v1 ? fast_exp2(fmaf(__uint_as_float(sr[cc][jj + 1]), sl2, -lse2)) : 0.f;
+              const float d0 = p0 * fmaf(__uint_as_float(dpr[cc][jj]), p.scale, -dlt_s);
+              const float d1 = p1 * fmaf(__uint_as_float(dpr[cc][jj + 1]), p.scale, -dlt_s);
+              pp[cc][jj / 2] = pack_bf16x2(p0, p1);
+              dd[cc][jj / 2] = pack_bf16x2(d0, d1);
+            }
+          }
+        }
+      }
+      NMB_PROF_LAP(1);  // computed P / dS
+      // The shared P / dS tiles are still being read by the previous tile's
+      // dV / dK MMAs; those ran while this tile's values were computed.
+      if (ok && i > 0 && !mbar_wait(pds_free, (i - 1) & 1, abort_flag, p.status, 50)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);
       if (L::kStageAlias && i > 0) {
         // The dQ staging tile aliases P / dS: the bulk reduce must have finished
         // reading it before anyone overwrites it.
-        if (r == 0) bulk_wait_read();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 0) bulk_wait_read();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
       }
-      uint8_t* sp = smem + L::kP;
-      uint8_t* sds = smem + L::kDS;
-#pragma unroll 1
-      for (int c = 0; c < (ok ? 4 : 0); ++c) {
-        uint32_t sr[32], dpr[32];
-        tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
-        tmem_ld_32x32(t_lane + kDPCol + c * 32, dpr);
-        tmem_ld_wait();
-        uint32_t pp[16], dd[16];
-        if (tile_full) {
+      if (ok) {
+        uint8_t* sp = smem + L::kP;
+        uint8_t* sds = smem + L::kDS;
 #pragma unroll
-          for (int jj = 0; jj < 32; jj += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[jj]), sl2, -lse2));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[jj + 1]), sl2, -lse2));
-            const float d0 = p0 * fmaf(__uint_as_float(dpr[jj]), p.scale, -dlt_s);
-            const float d1 = p1 * fmaf(__uint_as_float(dpr[jj + 1]), p.scale, -dlt_s);
-            pp[jj / 2] = pack_bf16x2(p0, p1);
-            dd[jj / 2] = pack_bf16x2(d0, d1);
-          }
-        } else {
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 2 + cc;
 #pragma unroll
-          for (int jj = 0; jj < 32; jj += 2) {
-            const bool v0 = c * 32 + jj <= limit;
-            const bool v1 = c * 32 + jj + 1 <= limit;
-            const float p0 = v0 ? fast_exp2(fmaf(__uint_as_float(sr[jj]), sl2, -lse2)) : 0.f;
-            const float p1 = v1 ? fast_exp2(fmaf(__uint_as_float(sr[jj + 1]), sl2, -lse2)) : 0.f;
-            const float d0 = p0 * fmaf(__uint_as_float(dpr[jj]), p.scale, -dlt_s);
-            const float d1 = p1 * fmaf(__uint_as_float(dpr[jj + 1]), p.scale, -dlt_s);
-            pp[jj / 2] = pack_bf16x2(p0, p1);
-            dd[jj / 2] = pack_bf16x2(d0, d1);
+          for (int t = 0; t < 4; ++t) {
+            const uint32_t off = (c >> 1) * 16384 + swz128_offset(r, (c & 1) * 4 + t);
+            *reinterpret_cast<uint4*>(sp + off) =
+                make_uint4(pp[cc][t * 4], pp[cc][t * 4 + 1], pp[cc][t * 4 + 2], pp[cc][t * 4 + 3]);
+            *reinterpret_cast<uint4*>(sds + off) =
+                make_uint4(dd[cc][t * 4], dd[cc][t * 4 + 1], dd[cc][t * 4 + 2], dd[cc][t * 4 + 3]);
           }
         }
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const uint32_t off = (c >> 1) * 16384 + swz128_offset(r, (c & 1) * 4 + t);
-          *reinterpret_cast<uint4*>(sp + off) = make_uint4(pp[t * 4], pp[t * 4 + 1], pp[t * 4 + 2], pp[t * 4 + 3]);
-          *reinterpret_cast<uint4*>(sds + off) = make_uint4(dd[t * 4], dd[t * 4 + 1], dd[t * 4 + 2], dd[t * 4 + 3]);
-        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(pds_full);
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      if (ok) mbar_arrive(pds_full);
-      if (ok && !mbar_wait(dq_full, i & 1, abort_flag, p.status, 49)) ok = false;
-      ok = __all_sync(0xffffffffu, ok);
-      tc_fence_after();
-      // dQ tile: TMEM -> fp32 staging tile (swizzled) -> ONE bulk reduce-add of
-      // the whole tile into the global accumulator, whose tiles use the same
-      // swizzled element order (attn_dq_store_kernel undoes it).
-      float* stage = reinterpret_cast<float*>(smem + L::kStage);
-      if (!L::kStageAlias) {
-        if (r == 0) bulk_wait_read();  // the previous tile's reduce has read the buffer
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
-      float* stage_row = stage + r * p.d;
-#pragma unroll 1
-      for (int c = 0; c < (ok ? HD / 32 : 0); ++c) {
-        uint32_t qr[32];
-        tmem_ld_32x32(t_lane + kDQCol + c * 32, qr);
-        tmem_ld_wait();
-        if (c * 32 < p.d) {
-#pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4) {
-            const int chunk = c * 8 + q4;                                   // 16-byte chunk of the row
-            const int phys = (chunk & ~7) | ((chunk ^ r) & 7);              // XOR swizzle inside 128-byte groups
-            *reinterpret_cast<uint4*>(stage_row + phys * 4) =
-                make_uint4(qr[q4 * 4], qr[q4 * 4 + 1], qr[q4 * 4 + 2], qr[q4 * 4 + 3]);
-          }
-        }
-      }
-      tc_fence_before();
-      if (ok) mbar_arrive(dq_empty);
-      fence_proxy_async_smem();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (r == 0 && ok) {
-        int rows_valid = p.Sq - q0;
-        if (rows_valid > 128) rows_valid = 128;
-        float* dq_tile = p.dq_acc + ((static_cast<long long>(b) * p.Hq + hq) * p.Sq + q0) * p.d;
-        bulk_reduce_add_f32(dq_tile, stage, static_cast<uint32_t>(rows_valid) * p.d * 4);
-        bulk_commit();
+      NMB_PROF_LAP(2);  // waited for the P / dS buffers, stored
+      // With two dQ accumulators the previous tile's dQ is written out while the
+      // tensor core works on this tile; with one, this tile's right away.
+      if (kAliasDQ) {
+        dq_out(i);
+      } else if (i > 0) {
+        dq_out(i - 1);
       }
     }
+    if (!kAliasDQ && n_iter > 0) dq_out(n_iter - 1);
+    NMB_PROF_STORE();
     bulk_wait_all();
-    // dK / dV of this tile: the last dq_full also covers their MMAs.
+    // dK / dV of this tile (rows = keys): wait for the last dV / dK MMAs.
+    if (ok && n_iter > 0 && !mbar_wait(pds_free, (n_iter - 1) & 1, abort_flag, p.status, 52)) ok = false;
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
     const int kv_row = kv_row0 + r;
-    if (ok && kv_row < p.chunk_len) {
-      // (when n_iter == 0 nothing was accumulated: write zeros)
-      const long long off = b * p.dkv_stride_b + static_cast<long long>(kv_row) * p.dkv_stride_s +
-                            hk * p.dkv_stride_h;
-      __nv_bfloat16* dk_row = p.dk[chunk] + off;
-      __nv_bfloat16* dv_row = p.dv[chunk] + off;
-      if (n_iter == 0) {
-        for (int c = 0; c < p.d; c += 8) {
-          *reinterpret_cast<uint4*>(dk_row + c) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(dv_row + c) = make_uint4(0, 0, 0, 0);
-        }
+    const long long off = b * p.dkv_stride_b + static_cast<long long>(kv_row) * p.dkv_stride_s + hk * p.dkv_stride_h;
+    constexpr int kHalfCols = HD / 2;
+    if (ok && n_iter == 0 && kv_row < p.chunk_len) {
+      // no query sees this tile: its gradient is zero
+      for (int c = half * kHalfCols; c < (half + 1) * kHalfCols && c < p.d; c += 8) {
+        *reinterpret_cast<uint4*>(p.dk[chunk] + off + c) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(p.dv[chunk] + off + c) = make_uint4(0, 0, 0, 0);
       }
     }
     if (ok && n_iter > 0) {
-      const long long off = b * p.dkv_stride_b + static_cast<long long>(kv_row) * p.dkv_stride_s +
-                            hk * p.dkv_stride_h;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* row = (which == 0 ? p.dv[chunk] : p.dk[chunk]) + off;
         const uint32_t col = which == 0 ? kDVCol : kDKCol;
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int cc = 0; cc < kHalfCols / 32; ++cc) {
+          const int c = half * (kHalfCols / 32) + cc;
           uint32_t ar[32];
           tmem_ld_32x32(t_lane + col + c * 32, ar);
           tmem_ld_wait();
@@ -728,7 +822,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -915,12 +1009,15 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq;
   p.chunk_len = chunk_len; p.n_chunks = n_chunks;
   p.d = d; p.q_pos0 = q_pos0; p.scale = scale; p.status = status;
+#ifdef NMB_ATTN_PROF
+  p.prof = reinterpret_cast<long long*>(delta) - 8;  // profiling builds: the caller over-allocates delta by 8 slots in front
+#endif
   dim3 grid(n_visible_kv_tiles, Hkv, B);
   cudaError_t e;
   if (d == 64) {
-    attn_bwd_kernel<64><<<grid, kAttnThreads, AttnBwdSmem<64>::kTotal, s>>>(p);
+    attn_bwd_kernel<64><<<grid, kBwdThreads, AttnBwdSmem<64>::kTotal, s>>>(p);
   } else {
-    attn_bwd_kernel<128><<<grid, kAttnThreads, AttnBwdSmem<128>::kTotal, s>>>(p);
+    attn_bwd_kernel<128><<<grid, kBwdThreads, AttnBwdSmem<128>::kTotal, s>>>(p);
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return 400 + e;
