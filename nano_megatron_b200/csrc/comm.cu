@@ -97,10 +97,11 @@ struct Vec16<float> {
 //   reduces the r-th sub-slice (reading all peers), then every rank copies the
 //   other ranks' reduced sub-slices.  Dependencies therefore stay between
 //   blocks of equal index, which is what `block_barrier` synchronises.
-template <typename T>
-__global__ void __launch_bounds__(512)
-allreduce_scale_kernel(PeerPtrs bufs, PeerPtrs pads, uint32_t* epochs, int channel, int rank, int n,
-                       long long n_vec, float scale, int* status, long long budget) {
+//   U = independent 16-byte loads in flight per thread (NVLink latency is ~2 us).
+template <typename T, int U>
+__device__ __forceinline__ void allreduce_scale_body(const PeerPtrs& bufs, const PeerPtrs& pads, uint32_t* epochs,
+                                                     int channel, int rank, int n, long long n_vec, float scale,
+                                                     int* status, long long budget) {
   using V = Vec16<T>;
   __shared__ uint32_t epoch_s;
   uint32_t* my_epoch = epochs + channel * kMaxBlocks + blockIdx.x;
@@ -114,7 +115,6 @@ allreduce_scale_kernel(PeerPtrs bufs, PeerPtrs pads, uint32_t* epochs, int chann
   const long long blk_len = blk_hi > blk_lo ? blk_hi - blk_lo : 0;
   const long long per_rank = (blk_len + n - 1) / n;
 
-  constexpr int U = 8;  // independent 16-byte loads in flight per thread (NVLink latency is ~2 us)
   bool ok = block_barrier(pads, channel, rank, n, e0 + 1, status, budget, 61);  // peers' inputs are ready
   if (ok) {
     const long long lo = blk_lo + per_rank * rank;
@@ -173,6 +173,26 @@ allreduce_scale_kernel(PeerPtrs bufs, PeerPtrs pads, uint32_t* epochs, int chann
   // nobody may overwrite a buffer a peer is still copying from
   block_barrier(pads, channel, rank, n, e0 + 3, status, budget, 63);
   if (threadIdx.x == 0) *my_epoch = e0 + 3;
+}
+
+// Latency-first variant: 512 threads, 8 loads in flight each; it fills the SMs
+// it runs on, so nothing else shares them.
+template <typename T>
+__global__ void __launch_bounds__(512)
+allreduce_scale_kernel(const __grid_constant__ PeerPtrs bufs, const __grid_constant__ PeerPtrs pads, uint32_t* epochs, int channel, int rank, int n,
+                       long long n_vec, float scale, int* status, long long budget) {
+  allreduce_scale_body<T, 8>(bufs, pads, epochs, channel, rank, n, n_vec, scale, status, budget);
+}
+
+// Overlap-first variant for gradient buckets reduced during backward: 256
+// threads of at most 64 registers (16 K registers per block), so that a block
+// fits beside a resident persistent GEMM CTA (320 threads x 144 registers)
+// instead of waiting for, or displacing, the compute kernels.
+template <typename T>
+__global__ void __maxnreg__(64)
+allreduce_scale_light_kernel(const __grid_constant__ PeerPtrs bufs, const __grid_constant__ PeerPtrs pads, uint32_t* epochs, int channel, int rank, int n,
+                             long long n_vec, float scale, int* status, long long budget) {
+  allreduce_scale_body<T, 4>(bufs, pads, epochs, channel, rank, n, n_vec, scale, status, budget);
 }
 
 // All-gather through peer stores: every rank writes its `n_vec` 16-byte vectors
@@ -321,6 +341,19 @@ static void fill(PeerPtrs& t, void* const* src, int n) {
   for (int i = 0; i < kMaxRanks; ++i) t.p[i] = i < n ? src[i] : nullptr;
 }
 
+// The overlap-first all-reduce asks for the same shared-memory carve-out as the
+// GEMM / attention kernels it runs beside: an SM only hosts CTAs of kernels
+// whose carve-out matches its current configuration, so with the default (small)
+// carve-out its blocks and the 190 KB GEMM CTAs would exclude each other.
+extern "C" int nmb_comm_configure() {
+  cudaError_t e = cudaFuncSetAttribute(allreduce_scale_light_kernel<__nv_bfloat16>,
+                                       cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(allreduce_scale_light_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+  return e == cudaSuccess ? 0 : 300 + e;
+}
+
 extern "C" int nmb_comm_limits(int* max_ranks, int* max_blocks, int* channels) {
   *max_ranks = kMaxRanks;
   *max_blocks = kMaxBlocks;
@@ -331,19 +364,28 @@ extern "C" int nmb_comm_limits(int* max_ranks, int* max_blocks, int* channels) {
 
 // bufs[n], pads[n]: per-rank device pointers (peer-mapped); numel elements of
 // bf16 (is_bf16) or fp32.  numel * elem_size must be a multiple of 16.
+// blocks < 0 selects the overlap-first variant with -blocks blocks.
 extern "C" int nmb_allreduce_scale(void* const* bufs, void* const* pads, void* epochs, int channel, int rank,
                                    int n, long long numel, int is_bf16, float scale, int blocks, int* status,
                                    long long budget_cycles, void* stream) {
   if (n < 1 || n > kMaxRanks || channel < 0 || channel >= kChannels) return kBadArgument;
   const int per = is_bf16 ? 8 : 4;
   if (numel % per != 0) return kBadArgument;
+  const bool light = blocks < 0;
+  if (light) blocks = -blocks;
   if (blocks < 1) blocks = 1;
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
   PeerPtrs b, p;
   fill(b, bufs, n);
   fill(p, pads, n);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (is_bf16)
+  if (light && is_bf16)
+    allreduce_scale_light_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel,
+                                                                      rank, n, numel / per, scale, status, budget_cycles);
+  else if (light)
+    allreduce_scale_light_kernel<float><<<blocks, 256, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
+                                                               numel / per, scale, status, budget_cycles);
+  else if (is_bf16)
     allreduce_scale_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
                                                                 numel / per, scale, status, budget_cycles);
   else

@@ -140,8 +140,8 @@ __global__ void norm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const _
 template <int V>
 __global__ void norm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                     const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
-                                    const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
-                                    float* __restrict__ partial, int rows, int rms) {
+                                    const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dx_add,
+                                    __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int rms) {
   constexpr int H = 256 * V;
   extern __shared__ float red[];  // [warps][2][H]
   const int lane = threadIdx.x & 31;
@@ -198,13 +198,25 @@ __global__ void norm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const 
     s1 = rms ? 0.f : warp_sum(s1) / H;
     s2 = warp_sum(s2) / H;
     uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * H);
+    const uint4* ar = reinterpret_cast<const uint4*>(dx_add + static_cast<size_t>(row) * H);
 #pragma unroll
     for (int c = 0; c < V; ++c) {
+      float add[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (dx_add != nullptr) {  // gradient of the residual branch that bypassed the norm
+        const uint4 au = ar[c * 32 + lane];
+        const uint32_t aa[4] = {au.x, au.y, au.z, au.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 a = unpack_bf16x2(aa[k]);
+          add[2 * k] = a.x;
+          add[2 * k + 1] = a.y;
+        }
+      }
       uint32_t o[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        o[k] = pack_bf16x2(rstd * (g[c][2 * k] * wv[c][2 * k] - s1 - xh[c][2 * k] * s2),
-                           rstd * (g[c][2 * k + 1] * wv[c][2 * k + 1] - s1 - xh[c][2 * k + 1] * s2));
+        o[k] = pack_bf16x2(rstd * (g[c][2 * k] * wv[c][2 * k] - s1 - xh[c][2 * k] * s2) + add[2 * k],
+                           rstd * (g[c][2 * k + 1] * wv[c][2 * k + 1] - s1 - xh[c][2 * k + 1] * s2) + add[2 * k + 1]);
       dr[c * 32 + lane] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
@@ -229,8 +241,10 @@ __global__ void norm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const 
 
 // Sums the per-block partial rows: 32 columns per block, 8 groups of partial
 // rows summed in parallel and combined through shared memory.
+// `accumulate`: add to what dgamma / dbeta already hold (gradient buffers).
 __global__ void norm_bwd_finish_kernel(const float* __restrict__ partial, int n_partial, int H,
-                                       __nv_bfloat16* __restrict__ dgamma, __nv_bfloat16* __restrict__ dbeta) {
+                                       __nv_bfloat16* __restrict__ dgamma, __nv_bfloat16* __restrict__ dbeta,
+                                       int accumulate) {
   __shared__ float red[8][32];
   const int cx = threadIdx.x & 31;
   const int px = threadIdx.x >> 5;
@@ -243,8 +257,11 @@ __global__ void norm_bwd_finish_kernel(const float* __restrict__ partial, int n_
     float s = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) s += red[k][cx];
-    if (col < H) dgamma[col] = __float2bfloat16(s);
-    else if (dbeta != nullptr) dbeta[col - H] = __float2bfloat16(s);
+    __nv_bfloat16* dst = col < H ? dgamma + col : (dbeta != nullptr ? dbeta + (col - H) : nullptr);
+    if (dst != nullptr) {
+      if (accumulate) s += __bfloat162float(*dst);
+      *dst = __float2bfloat16(s);
+    }
   }
 }
 
@@ -300,12 +317,19 @@ __global__ void norm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const _
 //   mode 0: out0[c] = sum_r dy[r,c]
 //   mode 1: out0[c] = sum_r dy[r,c] * xhat[r,c] (dgamma), out1[c] = sum_r dy[r,c] (dbeta)
 // Stage 1 writes partial[split][2][H] (fp32); stage 2 sums the splits and
-// stores / accumulates bf16.
+// stores / accumulates bf16.  With `fused_finish` stage 2 runs inside stage 1:
+// the block that arrives last on its column group's counter (all splits of the
+// 64 columns are then in memory) sums them, so one launch does the whole
+// reduction.  The counters return to zero, ready for the next launch (graph
+// replays included); launches that share the scratch must be stream-ordered.
 constexpr int kColSplit = 64;
+constexpr int kMaxColGroups = 1024;
+__device__ unsigned int g_col_arrivals[kMaxColGroups];
 
 __global__ void col_reduce_stage1(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                   const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
-                                  float* __restrict__ partial, int rows, int H, int ld, int mode, int rms) {
+                                  float* partial, int rows, int H, int ld, int mode, int rms, int fused_finish,
+                                  __nv_bfloat16* out0, __nv_bfloat16* out1, int accumulate) {
   // block = 32 lanes (column pairs) x 8 warps (rows); grid = (ceil(H/64), kColSplit)
   __shared__ float red[2][8][64];
   const int lane = threadIdx.x & 31;
@@ -342,6 +366,42 @@ __global__ void col_reduce_stage1(const __nv_bfloat16* __restrict__ dy, const __
     for (int wv = 0; wv < 8; ++wv) s += red[which][wv][col];
     const int cc = blockIdx.x * 64 + col;
     if (cc < H) partial[(static_cast<size_t>(blockIdx.y) * 2 + which) * H + cc] = s;
+    __threadfence();
+  }
+  if (!fused_finish) return;
+  __shared__ int is_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(&g_col_arrivals[blockIdx.x], 1u);
+    is_last = prev == gridDim.y - 1;
+    if (is_last) g_col_arrivals[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  {
+    // 2 x 64 sums of kColSplit partials: each half of the block takes half the splits
+    const int pair = threadIdx.x & 127;
+    const int half = threadIdx.x >> 7;
+    const int which = pair >> 6;
+    const int cc = blockIdx.x * 64 + (pair & 63);
+    float s = 0.f;
+    if (cc < H && (which == 0 || out1 != nullptr)) {
+#pragma unroll 8
+      for (int k = half * (kColSplit / 2); k < (half + 1) * (kColSplit / 2); ++k)
+        s += __ldcg(&partial[(static_cast<size_t>(k) * 2 + which) * H + cc]);
+    }
+    float* comb = &red[0][0][0];
+    if (half == 1) comb[pair] = s;
+    __syncthreads();
+    if (half == 0 && cc < H) {
+      s += comb[pair];
+      __nv_bfloat16* dst = which == 0 ? out0 : out1;
+      if (dst != nullptr) {
+        if (accumulate) s += __bfloat162float(dst[cc]);
+        dst[cc] = __float2bfloat16(s);
+      }
+    }
   }
 }
 
@@ -437,37 +497,41 @@ extern "C" int nmb_norm_configure() {
 }
 
 template <int V>
-static void launch_bwd_vec(const void* dy, const void* x, const void* w, const float* mean, const float* rstd, void* dx,
-                           float* partial, int rows, int rms, int blocks, cudaStream_t s) {
+static void launch_bwd_vec(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                           const void* dx_add, void* dx, float* partial, int rows, int rms, int blocks, cudaStream_t s) {
   norm_bwd_vec_kernel<V><<<blocks, 256, 8 * 2 * 256 * V * sizeof(float), s>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-      mean, rstd, static_cast<__nv_bfloat16*>(dx), partial, rows, rms);
+      mean, rstd, static_cast<const __nv_bfloat16*>(dx_add), static_cast<__nv_bfloat16*>(dx), partial, rows, rms);
 }
 
 // Fused backward: dx, dgamma, dbeta in one pass over dy and x.  Needs
 // H % 256 == 0, H <= 1024 (register budget) and 16-byte aligned rows; returns
 // -1 when the shape is not covered (callers then use the generic kernels).
-// `partial` is fp32 scratch of kNormBwdBlocks * 2 * H elements.
+// `partial` is fp32 scratch of kNormBwdBlocks * 2 * H elements.  `dx_add`
+// (optional, same shape as dx) is added to dx; `accumulate` adds the parameter
+// gradients to the contents of dgamma / dbeta instead of overwriting them.
 constexpr int kNormBwdBlocks = 148;
 extern "C" int nmb_norm_bwd_fused_blocks() { return kNormBwdBlocks; }
 
 extern "C" int nmb_norm_bwd_fused(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
-                                  void* dx, void* dgamma, void* dbeta, float* partial, int rows, int H, int rms,
-                                  void* stream) {
+                                  const void* dx_add, void* dx, void* dgamma, void* dbeta, float* partial, int rows,
+                                  int H, int rms, int accumulate, void* stream) {
   if (rows <= 0) return 0;
-  if (H % 256 != 0 || H > 1024 || !aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx)) return -1;
+  if (H % 256 != 0 || H > 1024 || !aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx) ||
+      !aligned16(dx_add))
+    return -1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int blocks = (rows + 7) / 8;
   if (blocks > kNormBwdBlocks) blocks = kNormBwdBlocks;
   switch (H / 256) {
-    case 1: launch_bwd_vec<1>(dy, x, w, mean, rstd, dx, partial, rows, rms, blocks, s); break;
-    case 2: launch_bwd_vec<2>(dy, x, w, mean, rstd, dx, partial, rows, rms, blocks, s); break;
-    case 3: launch_bwd_vec<3>(dy, x, w, mean, rstd, dx, partial, rows, rms, blocks, s); break;
-    case 4: launch_bwd_vec<4>(dy, x, w, mean, rstd, dx, partial, rows, rms, blocks, s); break;
+    case 1: launch_bwd_vec<1>(dy, x, w, mean, rstd, dx_add, dx, partial, rows, rms, blocks, s); break;
+    case 2: launch_bwd_vec<2>(dy, x, w, mean, rstd, dx_add, dx, partial, rows, rms, blocks, s); break;
+    case 3: launch_bwd_vec<3>(dy, x, w, mean, rstd, dx_add, dx, partial, rows, rms, blocks, s); break;
+    case 4: launch_bwd_vec<4>(dy, x, w, mean, rstd, dx_add, dx, partial, rows, rms, blocks, s); break;
     default: return -1;
   }
   norm_bwd_finish_kernel<<<2 * H / 32, 256, 0, s>>>(partial, blocks, H, static_cast<__nv_bfloat16*>(dgamma),
-                                                    static_cast<__nv_bfloat16*>(dbeta));
+                                                    static_cast<__nv_bfloat16*>(dbeta), accumulate);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + e;
 }
@@ -480,11 +544,14 @@ extern "C" int nmb_col_reduce(const void* dy, int ld, const void* x, const float
   if (H % 2 != 0 || ld % 2 != 0) return kBadArgument;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid((H + 63) / 64, kColSplit);
+  const int fused_finish = grid.x <= kMaxColGroups ? 1 : 0;
   col_reduce_stage1<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dy),
                                          static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows, H, ld,
-                                         mode, rms);
-  col_reduce_stage2<<<(H + 255) / 256, 256, 0, s>>>(partial, static_cast<__nv_bfloat16*>(out0),
-                                                    static_cast<__nv_bfloat16*>(out1), H, accumulate);
+                                         mode, rms, fused_finish, static_cast<__nv_bfloat16*>(out0),
+                                         static_cast<__nv_bfloat16*>(out1), accumulate);
+  if (!fused_finish)
+    col_reduce_stage2<<<(H + 255) / 256, 256, 0, s>>>(partial, static_cast<__nv_bfloat16*>(out0),
+                                                      static_cast<__nv_bfloat16*>(out1), H, accumulate);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + e;
 }

@@ -14,6 +14,7 @@ The reference has no counterpart: its only transport is ``torch.distributed``
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any, Callable, Optional
 
 import torch
@@ -25,6 +26,10 @@ from . import symmetric
 #: ~1 s at 1.9 GHz; a peer that never arrives ends the wait with a status code
 DEFAULT_BUDGET_CYCLES = 2_000_000_000
 CHANNEL_TP, CHANNEL_DP, CHANNEL_CP, CHANNEL_AUX = 0, 1, 2, 3
+# Grid of the gradient-bucket all-reduce.  Negative: the overlap-first kernel
+# with that many blocks (it shares SMs with the backward GEMMs instead of taking
+# them over); positive: the latency-first kernel.
+DDP_ALLREDUCE_BLOCKS = int(os.environ.get("NMB_DDP_AR_BLOCKS", "-148"))
 
 
 class _RawCuda:
@@ -134,7 +139,9 @@ class SymmetricWorkspace:
         native.check_rc(rc, "nmb_symm_barrier")
 
     def all_reduce_scale_(self, t: torch.Tensor, scale: float, *, channel: int = CHANNEL_DP, blocks: int = 128) -> None:
-        """In-place ``t = sum_over_ranks(t) * scale`` for a tensor from ``alloc_tensor``."""
+        """In-place ``t = sum_over_ranks(t) * scale`` for a tensor from ``alloc_tensor``.
+        ``blocks < 0`` selects the overlap-first kernel (256 threads x 64 registers
+        per block, ``-blocks`` blocks) that fits beside a resident GEMM CTA."""
         assert t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous()
         rc = native.lib().nmb_allreduce_scale(
             self.peer_table(t), self.pad.table(), native.ptr(self.epochs), ctypes.c_int(channel),
@@ -190,7 +197,7 @@ class SymmetricWorkspace:
             rc = native.lib().nmb_allreduce_scale(
                 table, pads, native.ptr(self.epochs), ctypes.c_int(CHANNEL_DP), ctypes.c_int(self.rank),
                 ctypes.c_int(self.size), ctypes.c_longlong(buf.numel()), ctypes.c_int(int(buf.dtype == torch.bfloat16)),
-                ctypes.c_float(1.0 / divisor), ctypes.c_int(128), native.ptr(self.status),
+                ctypes.c_float(1.0 / divisor), ctypes.c_int(DDP_ALLREDUCE_BLOCKS), native.ptr(self.status),
                 ctypes.c_longlong(self.budget), native.stream_ptr(self.device))
             native.check_rc(rc, "nmb_allreduce_scale")
             return True

@@ -167,16 +167,17 @@ class TPCausalSelfAttention(nn.Module):
 
     def _forward_native(self, x: Tensor, positions: Optional[Tensor], residual: Optional[Tensor]) -> Tensor:
         """bf16 GPU path: packed projection -> in-place views -> tcgen05 attention."""
-        from ..ops.attention import flash_attention
+        from ..ops.attention import flash_attention, flash_attention_packed, split_packed_qkv
 
         d = self.head_dim
         hq, hkv = self.local_num_heads, self.local_num_kv_heads
         if self.config.use_fused_qkv:
             qkv = self.qkv_proj(x)
             b, s, _ = qkv.shape
-            q = qkv[..., : hq * d].view(b, s, hq, d)
-            k = qkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
-            v = qkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
+            if self._cp_size == 1 and not (self.rotary_emb and positions is not None) and qkv.is_contiguous():
+                context = flash_attention_packed(qkv, hq, hkv, d, self.scale)
+                return self.out_proj(context.view(b, s, hq * d), residual=residual)
+            q, k, v = split_packed_qkv(qkv, hq, hkv, d)
         else:
             q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
             b, s, _ = q.shape
@@ -241,8 +242,11 @@ class TPTransformerBlock(nn.Module):
         return OF.layer_norm(x, weight, bias, self.layernorm_eps)
 
     def forward(self, x: Tensor, positions: Optional[Tensor] = None) -> Tensor:
-        resid1 = self.attn(self._apply_norm(x, self.ln1_weight, self.ln1_bias), positions=positions, residual=x)
-        return self.mlp(self._apply_norm(resid1, self.ln2_weight, self.ln2_bias), residual=resid1)
+        rms = self.config.normalization == "rmsnorm"
+        h, x = OF.norm_with_residual(x, self.ln1_weight, self.ln1_bias, self.layernorm_eps, rms)
+        resid1 = self.attn(h, positions=positions, residual=x)
+        h, resid1 = OF.norm_with_residual(resid1, self.ln2_weight, self.ln2_bias, self.layernorm_eps, rms)
+        return self.mlp(h, residual=resid1)
 
 
 class TPGPT(nn.Module):

@@ -57,19 +57,26 @@ def attn_fwd(q, k_chunks, v_chunks, scale: float, q_pos0: int = 0):
 
 def attn_bwd(q, k_chunks, v_chunks, out, dout, lse, scale: float, q_pos0: int = 0,
              dk_chunks: Optional[Sequence[torch.Tensor]] = None,
-             dv_chunks: Optional[Sequence[torch.Tensor]] = None):
+             dv_chunks: Optional[Sequence[torch.Tensor]] = None,
+             dq: Optional[torch.Tensor] = None):
     """Returns ``(dq, dk_chunks, dv_chunks)``.  ``dk_chunks[c]`` receives this
     rank's contribution to chunk ``c``; rows of chunks the queries cannot see
-    are left untouched (callers pass zero-filled or freshly visible buffers)."""
+    are left untouched (callers pass zero-filled or freshly visible buffers).
+    ``dq`` / ``dk_chunks`` / ``dv_chunks`` may be strided views (for instance
+    slices of one packed dQKV buffer); they are written in place."""
     b, sq, hq, d = q.shape
     chunk_len, hkv = k_chunks[0].shape[1], k_chunks[0].shape[2]
     n_chunks = len(k_chunks)
     if dout.stride(3) != 1:
         dout = dout.contiguous()
-    dq = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device)
+    if dq is None:
+        dq = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device)
     if dk_chunks is None:
-        dk_chunks = [torch.zeros((b, chunk_len, hkv, d), dtype=torch.bfloat16, device=q.device) for _ in range(n_chunks)]
-        dv_chunks = [torch.zeros_like(t) for t in dk_chunks]
+        # every key row is visible to some query: the kernel writes all of dK / dV
+        covered = n_chunks == 1 and q_pos0 + sq >= chunk_len
+        make = torch.empty if covered else torch.zeros
+        dk_chunks = [make((b, chunk_len, hkv, d), dtype=torch.bfloat16, device=q.device) for _ in range(n_chunks)]
+        dv_chunks = [make((b, chunk_len, hkv, d), dtype=torch.bfloat16, device=q.device) for _ in range(n_chunks)]
     delta = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
     dq_acc = torch.empty((b, sq, hq, d), dtype=torch.float32, device=q.device)
     n_tiles = _visible_kv_tiles(sq, q_pos0, chunk_len * n_chunks)
@@ -103,6 +110,66 @@ class _FlashAttention(torch.autograd.Function):
 def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
     """Causal attention over ``[B, S, heads, d]`` views; returns ``[B, S, Hq, d]``."""
     return _FlashAttention.apply(q, k, v, float(scale))
+
+
+def _split_packed(qkv: torch.Tensor, hq: int, hkv: int, d: int):
+    b, s, _ = qkv.shape
+    q = qkv[..., : hq * d].view(b, s, hq, d)
+    k = qkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+    v = qkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
+    return q, k, v
+
+
+class _FlashAttentionPacked(torch.autograd.Function):
+    """Attention straight from / to the packed ``[B, S, (Hq + 2 Hkv) d]`` tensor of a
+    fused QKV projection: forward reads its three slices in place, backward has
+    the kernels write dQ, dK and dV into the slices of ONE gradient buffer, so no
+    slice-gradient zero-fill / copy / add kernels run around the attention."""
+
+    @staticmethod
+    def forward(ctx, qkv, hq, hkv, d, scale):
+        q, k, v = _split_packed(qkv, hq, hkv, d)
+        out, lse = attn_fwd(q, [k], [v], scale, 0)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.meta = (hq, hkv, d, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        hq, hkv, d, scale = ctx.meta
+        q, k, v = _split_packed(qkv, hq, hkv, d)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = _split_packed(dqkv, hq, hkv, d)
+        attn_bwd(q, [k], [v], out, dout, lse, scale, 0, dk_chunks=[dk], dv_chunks=[dv], dq=dq)
+        return dqkv, None, None, None, None
+
+
+def flash_attention_packed(qkv: torch.Tensor, hq: int, hkv: int, d: int, scale: float) -> torch.Tensor:
+    """Causal attention over a packed, contiguous ``[B, S, (Hq + 2 Hkv) d]`` tensor
+    (query heads, then key heads, then value heads); returns ``[B, S, Hq, d]``."""
+    assert qkv.dim() == 3 and qkv.is_contiguous() and qkv.shape[-1] == (hq + 2 * hkv) * d
+    return _FlashAttentionPacked.apply(qkv, hq, hkv, d, float(scale))
+
+
+class _SplitPacked(torch.autograd.Function):
+    """``qkv -> (q, k, v)`` views whose gradients are joined by one concatenation
+    kernel instead of three zero-fills, three strided copies and two adds."""
+
+    @staticmethod
+    def forward(ctx, qkv, hq, hkv, d):
+        ctx.meta = (hq, hkv, d)
+        return _split_packed(qkv, hq, hkv, d)
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        b, s = dq.shape[0], dq.shape[1]
+        return torch.cat([dq.reshape(b, s, -1), dk.reshape(b, s, -1), dv.reshape(b, s, -1)], dim=-1), None, None, None
+
+
+def split_packed_qkv(qkv: torch.Tensor, hq: int, hkv: int, d: int):
+    """Differentiable ``[B, S, (Hq + 2 Hkv) d] -> q, k, v`` views (``[B, S, heads, d]``)."""
+    return _SplitPacked.apply(qkv, hq, hkv, d)
 
 
 def attention_supported(d: int) -> bool:

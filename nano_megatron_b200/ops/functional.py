@@ -202,34 +202,80 @@ def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, *, residual
 
 
 # -------------------------------------------------------------------- norm --
+def _norm_grad_targets(w_param, b_param, want_bias: bool):
+    """The parameters' persistent gradient buffers when the norm backward may add
+    to them directly (bf16 ``main_grad`` on every parameter involved, none of
+    them reduced over the sequence-parallel group by an autograd hook)."""
+    params = [w_param] + ([b_param] if want_bias else [])
+    bufs = []
+    for p in params:
+        main = getattr(p, "main_grad", None)
+        if main is None or main.dtype != torch.bfloat16 or getattr(p, "_nmb_sp_replicated", False):
+            return None
+        bufs.append(main)
+    return (bufs[0], bufs[1] if want_bias else None), params
+
+
 class _NormFn(torch.autograd.Function):
+    """LayerNorm / RMSNorm.  With ``passthrough`` the input is also returned
+    unchanged as a second output for the residual connection, so that backward
+    receives the residual branch's gradient together with dy and adds it inside
+    the dx kernel (no separate accumulation kernel)."""
+
     @staticmethod
-    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], eps: float, rms: bool):
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], eps: float, rms: bool, passthrough: bool):
         y, mean, rstd = kernels.norm_fwd(x, weight, bias, eps, rms)
         ctx.save_for_backward(x, weight, mean, rstd)
         ctx.rms = rms
         ctx.params = (weight, bias)
+        ctx.passthrough = passthrough
+        if passthrough:
+            return y, x.view_as(x)
         return y
 
     @staticmethod
-    def backward(ctx, dy: Tensor):
+    def backward(ctx, dy: Optional[Tensor], dres: Optional[Tensor] = None):
         x, weight, mean, rstd = ctx.saved_tensors
         w_param, b_param = ctx.params
-        dx, dw, db = kernels.norm_bwd(dy, x, weight, mean, rstd, ctx.rms, want_bias=b_param is not None and not ctx.rms)
-        return dx, dw, db, None, None
+        want_bias = b_param is not None and not ctx.rms
+        if dy is None:  # only the residual branch was used
+            return dres, None, None, None, None, None
+        if dres is not None and (dres.shape != x.shape or not dres.is_contiguous()):
+            dres = dres.expand_as(x).contiguous()
+        targets = _norm_grad_targets(w_param, b_param, want_bias)
+        if targets is not None:
+            bufs, params = targets
+            dx, _, _ = kernels.norm_bwd(dy, x, weight, mean, rstd, ctx.rms, dx_add=dres, want_bias=want_bias,
+                                        grad_out=bufs)
+            for p in params:
+                ready = getattr(p, "_nmb_grad_ready", None)
+                if ready is not None:
+                    ready()
+            return dx, None, None, None, None, None
+        dx, dw, db = kernels.norm_bwd(dy, x, weight, mean, rstd, ctx.rms, dx_add=dres, want_bias=want_bias)
+        return dx, dw, db, None, None, None
 
 
 def layer_norm(x: Tensor, weight: Tensor, bias: Optional[Tensor], eps: float) -> Tensor:
     if use_native(x) and x.shape[-1] % 2 == 0:
-        return _NormFn.apply(x, weight, bias, eps, False)
+        return _NormFn.apply(x, weight, bias, eps, False, False)
     return F.layer_norm(x, (x.shape[-1],), weight=weight, bias=bias, eps=eps)
 
 
 def rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
     if use_native(x) and x.shape[-1] % 2 == 0:
-        return _NormFn.apply(x, weight, None, eps, True)
+        return _NormFn.apply(x, weight, None, eps, True, False)
     from ..reference.layers import rms_norm as _rms
     return _rms(x, weight, eps)
+
+
+def norm_with_residual(x: Tensor, weight: Tensor, bias: Optional[Tensor], eps: float, rms: bool):
+    """``(norm(x), x)`` for a pre-norm residual block: use the second value for
+    the residual connection.  On the native path its gradient is folded into the
+    norm's dx kernel."""
+    if use_native(x) and x.shape[-1] % 2 == 0 and x.is_contiguous():
+        return _NormFn.apply(x, weight, None if rms else bias, eps, rms, True)
+    return (rms_norm(x, weight, eps) if rms else layer_norm(x, weight, bias, eps)), x
 
 
 # ------------------------------------------------------------- activations --

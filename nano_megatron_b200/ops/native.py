@@ -45,7 +45,8 @@ def _configure_current_device(loaded: ctypes.CDLL) -> None:
     dev = torch.cuda.current_device()
     if dev in _configured_devices:
         return
-    for fn in (loaded.nmb_gemm_configure, loaded.nmb_attn_configure, loaded.nmb_norm_configure):
+    for fn in (loaded.nmb_gemm_configure, loaded.nmb_attn_configure, loaded.nmb_norm_configure,
+               loaded.nmb_comm_configure):
         rc = fn()
         if rc != 0:
             raise NativeKernelError(f"kernel configuration failed with code {rc} on device {dev}")

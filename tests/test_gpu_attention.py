@@ -56,6 +56,38 @@ def test_flash_fwd_bwd(b, s, hq, hkv, d):
     assert err < 5e-2 * max(1.0, ref_in.grad.abs().max().item()), err
 
 
+@pytest.mark.parametrize("b,s,hq,hkv,d", [(2, 256, 4, 4, 64), (1, 200, 4, 2, 64), (1, 256, 2, 2, 128)])
+def test_flash_packed_matches_reference_and_writes_one_gradient_buffer(b, s, hq, hkv, d):
+    """The packed entry point (dQ / dK / dV written into slices of one buffer)."""
+    from nano_megatron_b200.ops import native
+    from nano_megatron_b200.ops.attention import flash_attention_packed, split_packed_qkv
+
+    torch.manual_seed(1)
+    scale = 1.0 / math.sqrt(d)
+    width = (hq + 2 * hkv) * d
+    qkv = torch.randn(b, s, width, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    out = flash_attention_packed(qkv, hq, hkv, d, scale)
+    ref_in = qkv.detach().float().requires_grad_(True)
+    rq = ref_in[..., : hq * d].view(b, s, hq, d)
+    rk = ref_in[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+    rv = ref_in[..., (hq + hkv) * d:].view(b, s, hkv, d)
+    ref = _ref(rq, rk, rv, scale)
+    assert (out.float() - ref).abs().max().item() < 2e-2
+    g = torch.randn_like(ref)
+    ref.backward(g)
+    out.backward(g.to(torch.bfloat16))
+    torch.cuda.synchronize()
+    native.check_status()
+    bound = 5e-2 * max(1.0, ref_in.grad.abs().max().item())
+    assert (qkv.grad.float() - ref_in.grad).abs().max().item() < bound
+    # the differentiable split (one concatenation in backward) gives the same gradient
+    qkv2 = qkv.detach().clone().requires_grad_(True)
+    q, k, v = split_packed_qkv(qkv2, hq, hkv, d)
+    (q.float().sum() * 2 + k.float().sum() * 3 + v.float().sum() * 5).backward()
+    expect = torch.cat([torch.full((hq * d,), 2.0), torch.full((hkv * d,), 3.0), torch.full((hkv * d,), 5.0)]).cuda()
+    assert torch.equal(qkv2.grad.float(), expect.expand(b, s, width))
+
+
 def test_flash_chunked_query_offset():
     """Simulated context-parallel rank 1 of 2: queries are the second half."""
     from nano_megatron_b200.ops import native

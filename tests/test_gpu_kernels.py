@@ -37,6 +37,58 @@ def test_norm_fwd_bwd(rows, h, rms):
         assert (b.grad.float() - bf.grad).abs().max().item() < 2e-2 * max(1.0, bf.grad.abs().max().item())
 
 
+@pytest.mark.parametrize("rows,h", [(512, 1024), (300, 1536)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_with_residual_folds_branch_gradient_and_accumulates_param_grads(rows, h, rms):
+    """y = f(norm(x)) + x: the residual gradient is added inside the dx kernel and
+    dgamma / dbeta are accumulated into the parameters' persistent buffers."""
+    from nano_megatron_b200.ops import functional as OF
+    from nano_megatron_b200.reference.layers import rms_norm
+
+    torch.manual_seed(0)
+    x, w, b = _bf(rows, h), _bf(h) * 0.5 + 1, _bf(h)
+    x.requires_grad_(True); w.requires_grad_(True); b.requires_grad_(True)
+    seed_w, seed_b = _bf(h), _bf(h)
+    fired = []
+    for p, seed in ((w, seed_w), (b, seed_b)):
+        p.main_grad = seed.clone()
+        p._nmb_grad_ready = (lambda p=p: fired.append(p))
+    mult = _bf(rows, h)
+    y, xr = OF.norm_with_residual(x, w, b, 1e-5, rms)
+    out = y * mult + xr
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    nf = rms_norm(xf, wf, 1e-5) if rms else F.layer_norm(xf, (h,), wf, bf, 1e-5)
+    ref = nf * mult.float() + xf
+    g = _bf(rows, h)
+    out.backward(g)
+    ref.backward(g.float())
+    assert (x.grad.float() - xf.grad).abs().max().item() < 5e-2 * max(1.0, xf.grad.abs().max().item())
+    assert w.grad is None and fired[0] is w
+    expect_w = seed_w.float() + wf.grad
+    assert (w.main_grad.float() - expect_w).abs().max().item() < 3e-2 * max(1.0, expect_w.abs().max().item())
+    if not rms:
+        assert b.grad is None and fired[1] is b
+        expect_b = seed_b.float() + bf.grad
+        assert (b.main_grad.float() - expect_b).abs().max().item() < 3e-2 * max(1.0, expect_b.abs().max().item())
+
+
+@pytest.mark.parametrize("rows,h,acc", [(4096, 4096, False), (1000, 1024, True), (33, 130, False), (512, 3072, True)])
+def test_col_sum_single_launch_and_repeatable(rows, h, acc):
+    """Bias-gradient column sum; the in-kernel finish must leave its arrival
+    counters clean, so a second call gives the same answer."""
+    from nano_megatron_b200.ops import kernels
+
+    torch.manual_seed(0)
+    dy = _bf(rows, h)
+    ref = dy.float().sum(0)
+    for _ in range(2):
+        seed = _bf(h)
+        out = seed.clone()
+        kernels.col_sum(dy, out=out, accumulate=acc)
+        expect = ref + seed.float() if acc else ref
+        assert (out.float() - expect).abs().max().item() < 2e-2 * max(1.0, expect.abs().max().item())
+
+
 @pytest.mark.parametrize("n,v", [(64, 128), (1000, 50304), (33, 1000)])
 def test_cross_entropy_single_rank(n, v):
     from nano_megatron_b200.ops import functional as OF
