@@ -929,6 +929,16 @@ extern "C" int nmb_attn_configure() {
   if (e != cudaSuccess) return 300 + e;
   e = cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnBwdSmem<128>::kTotal);
   if (e != cudaSuccess) return 300 + e;
+  // same carve-out as the GEMMs and the overlapped communication kernels
+  const int carve = cudaSharedmemCarveoutMaxShared;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout, carve);
+  if (e != cudaSuccess) return 300 + e;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, carve);
+  if (e != cudaSuccess) return 300 + e;
+  e = cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout, carve);
+  if (e != cudaSuccess) return 300 + e;
+  e = cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, carve);
+  if (e != cudaSuccess) return 300 + e;
   return 0;
 }
 

@@ -184,12 +184,16 @@ allreduce_scale_kernel(const __grid_constant__ PeerPtrs bufs, const __grid_const
   allreduce_scale_body<T, 8>(bufs, pads, epochs, channel, rank, n, n_vec, scale, status, budget);
 }
 
-// Overlap-first variant for gradient buckets reduced during backward: 256
-// threads of at most 64 registers (16 K registers per block), so that a block
-// fits beside a resident persistent GEMM CTA (320 threads x 144 registers)
-// instead of waiting for, or displacing, the compute kernels.
+// Overlap-first variant for gradient buckets reduced during backward.  A block
+// must fit beside a resident persistent GEMM CTA (10 warps x 144 registers)
+// instead of waiting for, or displacing, it.  The register file is split over
+// the four SM sub-partitions (16 K registers each) and warps are dealt to them
+// round-robin, so the GEMM's 10 warps leave 16384 - 3 * 4608 = 2560 registers
+// on the fullest sub-partitions: room for ONE more warp of at most 80
+// registers per thread there, i.e. a block of 4 warps.
+constexpr int kLightThreads = 128;
 template <typename T>
-__global__ void __maxnreg__(64)
+__global__ void __maxnreg__(80)
 allreduce_scale_light_kernel(const __grid_constant__ PeerPtrs bufs, const __grid_constant__ PeerPtrs pads, uint32_t* epochs, int channel, int rank, int n,
                              long long n_vec, float scale, int* status, long long budget) {
   allreduce_scale_body<T, 4>(bufs, pads, epochs, channel, rank, n, n_vec, scale, status, budget);
@@ -345,6 +349,14 @@ static void fill(PeerPtrs& t, void* const* src, int n) {
 // GEMM / attention kernels it runs beside: an SM only hosts CTAs of kernels
 // whose carve-out matches its current configuration, so with the default (small)
 // carve-out its blocks and the 190 KB GEMM CTAs would exclude each other.
+// Dynamic shared memory requested (and left unused) by the overlap-first kernel.
+static int g_light_smem_bytes = 0;
+extern "C" int nmb_comm_set_light_smem(int bytes) {
+  if (bytes < 0 || bytes > 32 * 1024) return kBadArgument;
+  g_light_smem_bytes = bytes;
+  return 0;
+}
+
 extern "C" int nmb_comm_configure() {
   cudaError_t e = cudaFuncSetAttribute(allreduce_scale_light_kernel<__nv_bfloat16>,
                                        cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -380,10 +392,10 @@ extern "C" int nmb_allreduce_scale(void* const* bufs, void* const* pads, void* e
   fill(p, pads, n);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (light && is_bf16)
-    allreduce_scale_light_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel,
+    allreduce_scale_light_kernel<__nv_bfloat16><<<blocks, kLightThreads, g_light_smem_bytes, s>>>(b, p, static_cast<uint32_t*>(epochs), channel,
                                                                       rank, n, numel / per, scale, status, budget_cycles);
   else if (light)
-    allreduce_scale_light_kernel<float><<<blocks, 256, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
+    allreduce_scale_light_kernel<float><<<blocks, kLightThreads, g_light_smem_bytes, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
                                                                numel / per, scale, status, budget_cycles);
   else if (is_bf16)
     allreduce_scale_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,

@@ -676,6 +676,13 @@ template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int configure_gemm() {
   cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN, STAGES>::kTotal + 1024);
+  // Every large kernel of the library asks for the maximum shared-memory
+  // carve-out, and so do the communication kernels meant to run beside them: an
+  // SM keeps one carve-out at a time, so kernels that prefer different ones
+  // cannot share it and would serialise instead of overlapping.
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
   return e == cudaSuccess ? 0 : 300 + static_cast<int>(e);
 }
 

@@ -120,12 +120,16 @@ class _LinearGeluSplitFn(torch.autograd.Function):
         out_shape = (*x.shape[:-1], n)
         act = act.view(out_shape)
         ctx.mark_non_differentiable(act)
+        # no zero-filled gradient tensor for the non-differentiable side output
+        ctx.set_materialize_grads(False)
         return pre.view(out_shape), act
 
     @staticmethod
-    def backward(ctx, dpre: Tensor, _dact):
+    def backward(ctx, dpre: Optional[Tensor], _dact):
         x2, weight = ctx.saved_tensors
         w_param, b_param = ctx.params
+        if dpre is None:
+            return None, None, None
         dz = _rows(dpre, weight.shape[0])
         dx = gemm_bf16(dz, weight, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
         dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dz, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
