@@ -265,8 +265,29 @@ def main() -> int:
         if runner.note:
             out["note"] = runner.note
         emit(out)
+    # The result is out.  Tear down in order, but never let teardown (NCCL
+    # communicator destruction, unmapping peer memory, interpreter finalisers)
+    # hold the job: a timer ends the process if close() stalls, and the process
+    # leaves without running finalisers once close() has returned.
+    barrier()
+    _arm_exit_timer(60.0)
     runner.close()
-    return 0
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
+def _arm_exit_timer(seconds: float) -> None:
+    import threading
+
+    def fire() -> None:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
 
 
 class B200Runner:

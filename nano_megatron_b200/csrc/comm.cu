@@ -346,17 +346,9 @@ static void fill(PeerPtrs& t, void* const* src, int n) {
 }
 
 // The overlap-first all-reduce asks for the same shared-memory carve-out as the
-// GEMM / attention kernels it runs beside: an SM only hosts CTAs of kernels
-// whose carve-out matches its current configuration, so with the default (small)
-// carve-out its blocks and the 190 KB GEMM CTAs would exclude each other.
-// Dynamic shared memory requested (and left unused) by the overlap-first kernel.
-static int g_light_smem_bytes = 0;
-extern "C" int nmb_comm_set_light_smem(int bytes) {
-  if (bytes < 0 || bytes > 32 * 1024) return kBadArgument;
-  g_light_smem_bytes = bytes;
-  return 0;
-}
-
+// GEMM / attention kernels it runs beside: an SM keeps one carve-out at a time,
+// so with the default (small) carve-out its blocks and the 190 KB GEMM CTAs
+// would exclude each other.
 extern "C" int nmb_comm_configure() {
   cudaError_t e = cudaFuncSetAttribute(allreduce_scale_light_kernel<__nv_bfloat16>,
                                        cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -392,10 +384,10 @@ extern "C" int nmb_allreduce_scale(void* const* bufs, void* const* pads, void* e
   fill(p, pads, n);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (light && is_bf16)
-    allreduce_scale_light_kernel<__nv_bfloat16><<<blocks, kLightThreads, g_light_smem_bytes, s>>>(b, p, static_cast<uint32_t*>(epochs), channel,
+    allreduce_scale_light_kernel<__nv_bfloat16><<<blocks, kLightThreads, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel,
                                                                       rank, n, numel / per, scale, status, budget_cycles);
   else if (light)
-    allreduce_scale_light_kernel<float><<<blocks, kLightThreads, g_light_smem_bytes, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
+    allreduce_scale_light_kernel<float><<<blocks, kLightThreads, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
                                                                numel / per, scale, status, budget_cycles);
   else if (is_bf16)
     allreduce_scale_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,

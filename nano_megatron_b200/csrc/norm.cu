@@ -405,6 +405,149 @@ __global__ void col_reduce_stage1(const __nv_bfloat16* __restrict__ dy, const __
   }
 }
 
+// Vector form of stage 1 (+ in-kernel finish) for H % 8 == 0 and 16-byte
+// aligned rows: a warp covers 256 columns with one 16-byte load per lane and
+// keeps four rows in flight; block (g, s) reduces rows s*8+w, s*8+w+8*S, ... of
+// column group g; the last block of a column group to finish adds the S
+// partial rows with float4 loads (4 x 64 threads, one quarter of the splits
+// each) and stores / accumulates the bf16 result.
+__global__ void __launch_bounds__(256)
+col_reduce_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                      const float* __restrict__ mean_in, const float* __restrict__ rstd_in, float* partial,
+                      int rows, int H, int ld, int mode, int rms, __nv_bfloat16* out0, __nv_bfloat16* out1,
+                      int accumulate) {
+  __shared__ __align__(16) float red[2][8][256];
+  __shared__ int is_last;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int S = gridDim.y;
+  const int c = blockIdx.x * 256 + lane * 8;
+  float a[8], b[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a[k] = b[k] = 0.f;
+  if (c < H) {
+    const int stride = S * 8;
+    for (int r0 = blockIdx.y * 8 + warp; r0 < rows; r0 += 4 * stride) {
+      uint4 g[4], v[4];
+      float m[4], rs[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u * stride;
+        g[u] = make_uint4(0, 0, 0, 0);
+        v[u] = make_uint4(0, 0, 0, 0);
+        m[u] = 0.f;
+        rs[u] = 0.f;
+        if (r < rows) {
+          g[u] = *reinterpret_cast<const uint4*>(dy + static_cast<size_t>(r) * ld + c);
+          if (mode == 1) {
+            v[u] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H + c);
+            m[u] = rms ? 0.f : mean_in[r];
+            rs[u] = rstd_in[r];
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t gg[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+        const uint32_t vv[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 gf = unpack_bf16x2(gg[k]);
+          if (mode == 1) {
+            const float2 xf = unpack_bf16x2(vv[k]);
+            a[2 * k] += gf.x * (xf.x - m[u]) * rs[u];
+            a[2 * k + 1] += gf.y * (xf.y - m[u]) * rs[u];
+            b[2 * k] += gf.x;
+            b[2 * k + 1] += gf.y;
+          } else {
+            a[2 * k] += gf.x;
+            a[2 * k + 1] += gf.y;
+          }
+        }
+      }
+    }
+  }
+  float4* ra = reinterpret_cast<float4*>(&red[0][warp][lane * 8]);
+  float4* rb = reinterpret_cast<float4*>(&red[1][warp][lane * 8]);
+  ra[0] = make_float4(a[0], a[1], a[2], a[3]);
+  ra[1] = make_float4(a[4], a[5], a[6], a[7]);
+  rb[0] = make_float4(b[0], b[1], b[2], b[3]);
+  rb[1] = make_float4(b[4], b[5], b[6], b[7]);
+  __syncthreads();
+  {
+    const int col = threadIdx.x;  // 256 columns of this group
+    const int cc = blockIdx.x * 256 + col;
+    if (cc < H) {
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int wv = 0; wv < 8; ++wv) {
+        s0 += red[0][wv][col];
+        s1 += red[1][wv][col];
+      }
+      partial[(static_cast<size_t>(blockIdx.y) * 2) * H + cc] = s0;
+      if (mode == 1) partial[(static_cast<size_t>(blockIdx.y) * 2 + 1) * H + cc] = s1;
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(&g_col_arrivals[blockIdx.x], 1u);
+    is_last = prev == gridDim.y - 1;
+    if (is_last) g_col_arrivals[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int quarter = threadIdx.x >> 6;           // which quarter of the splits
+  const int c4 = (threadIdx.x & 63) * 4;          // 4 columns per thread
+  const int cc = blockIdx.x * 256 + c4;
+  const int n_out = mode == 1 ? 2 : 1;
+  float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+  if (cc < H) {
+    for (int which = 0; which < n_out; ++which) {
+#pragma unroll 4
+      for (int k = quarter; k < S; k += 4) {
+        const float4 p4 = __ldcg(reinterpret_cast<const float4*>(&partial[(static_cast<size_t>(k) * 2 + which) * H + cc]));
+        acc[which].x += p4.x;
+        acc[which].y += p4.y;
+        acc[which].z += p4.z;
+        acc[which].w += p4.w;
+      }
+    }
+  }
+  float4* comb = reinterpret_cast<float4*>(&red[0][0][0]);  // [which][quarter][64]
+  comb[(0 * 4 + quarter) * 64 + (threadIdx.x & 63)] = acc[0];
+  comb[(1 * 4 + quarter) * 64 + (threadIdx.x & 63)] = acc[1];
+  __syncthreads();
+  if (threadIdx.x < 64 * n_out && blockIdx.x * 256 + (threadIdx.x & 63) * 4 < H) {
+    const int which = threadIdx.x >> 6;
+    const int idx = threadIdx.x & 63;
+    float4 t = comb[(which * 4) * 64 + idx];
+#pragma unroll
+    for (int q = 1; q < 4; ++q) {
+      const float4 o = comb[(which * 4 + q) * 64 + idx];
+      t.x += o.x;
+      t.y += o.y;
+      t.z += o.z;
+      t.w += o.w;
+    }
+    __nv_bfloat16* dst = which == 0 ? out0 : out1;
+    if (dst != nullptr) {
+      dst += blockIdx.x * 256 + idx * 4;  // H % 8 == 0: all four columns exist
+      float r4[4] = {t.x, t.y, t.z, t.w};
+      if (accumulate) {
+        const uint2 old = *reinterpret_cast<const uint2*>(dst);
+        const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y);
+        r4[0] += o0.x;
+        r4[1] += o0.y;
+        r4[2] += o1.x;
+        r4[3] += o1.y;
+      }
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(r4[0], r4[1]), pack_bf16x2(r4[2], r4[3]));
+    }
+  }
+}
+
 __global__ void col_reduce_stage2(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out0,
                                   __nv_bfloat16* __restrict__ out1, int H, int accumulate) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -543,6 +686,19 @@ extern "C" int nmb_col_reduce(const void* dy, int ld, const void* x, const float
   if (rows <= 0 || H <= 0) return 0;
   if (H % 2 != 0 || ld % 2 != 0) return kBadArgument;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (H % 8 == 0 && ld % 8 == 0 && aligned16(dy) && (mode != 1 || aligned16(x)) && (H + 255) / 256 <= kMaxColGroups &&
+      (out0 == nullptr || (reinterpret_cast<uintptr_t>(out0) & 7) == 0) &&
+      (out1 == nullptr || (reinterpret_cast<uintptr_t>(out1) & 7) == 0)) {
+    const int groups = (H + 255) / 256;
+    int split = 8;  // at least two blocks per SM, at most kColSplit partial rows
+    while (split < kColSplit && groups * split < 2 * sm_count()) split *= 2;
+    while (split > 1 && split * 8 > rows) split /= 2;
+    col_reduce_vec_kernel<<<dim3(groups, split), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows, H, ld,
+        mode, rms, static_cast<__nv_bfloat16*>(out0), static_cast<__nv_bfloat16*>(out1), accumulate);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : 400 + e;
+  }
   dim3 grid((H + 63) / 64, kColSplit);
   const int fused_finish = grid.x <= kMaxColGroups ? 1 : 0;
   col_reduce_stage1<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(dy),

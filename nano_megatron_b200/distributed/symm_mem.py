@@ -64,12 +64,34 @@ class SymmetricWorkspace:
         self.max_ranks, self.max_blocks, self.channels = mr.value, mb.value, ch.value
         if self.size > self.max_ranks:
             raise RuntimeError(f"group of {self.size} ranks exceeds the kernel limit of {self.max_ranks}")
+        self._closed = False
         self._allocs: list[SymmetricAllocation] = []
         self._by_ptr: dict[int, tuple[SymmetricAllocation, int]] = {}
         self.pad = self._alloc_raw(self.channels * self.max_blocks * self.max_ranks * 4)
         self.epochs = torch.zeros(self.channels * self.max_blocks, dtype=torch.int32, device=self.device)
         self.status = native.status_word(self.device)
         dist.barrier(group=group)
+
+    def close(self) -> None:
+        """Collective, orderly release: every rank unmaps its peers' buffers, the
+        group meets, then every rank frees its own.  Tensors handed out by this
+        workspace must not be used afterwards."""
+        if self._closed:
+            return
+        self._closed = True
+        lib = native.lib()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)          # nobody's kernels still touch a peer buffer
+        for alloc in self._allocs:
+            for r, ptr in enumerate(alloc.peer_ptrs):
+                if r != self.rank and ptr:
+                    lib.nmb_symm_close(ctypes.c_void_p(ptr))
+        dist.barrier(group=self.group)          # nobody still maps my buffers
+        for alloc in self._allocs:
+            alloc.bytes = None
+            lib.nmb_symm_free(ctypes.c_void_p(alloc.local_ptr))
+        self._allocs.clear()
+        self._by_ptr.clear()
 
     # ------------------------------------------------------------ allocation --
     def _alloc_raw(self, nbytes: int) -> SymmetricAllocation:

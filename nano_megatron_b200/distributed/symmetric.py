@@ -23,6 +23,18 @@ def clear() -> None:
     _WORKSPACES.clear()
 
 
+def close_all() -> None:
+    """Release every registered workspace (collective over each one's group, in
+    registration order, which is the same on all ranks) and forget them."""
+    seen = set()
+    for ws in list(_WORKSPACES.values()):
+        if id(ws) in seen:
+            continue
+        seen.add(id(ws))
+        ws.close()
+    _WORKSPACES.clear()
+
+
 def cp_flash_attention_peer(q, k, v, scale, ws, cp_rank, cp_size):
     from .symm_ops import cp_flash_attention_peer as impl
     return impl(q, k, v, scale, ws, cp_rank, cp_size)

@@ -155,6 +155,10 @@ def is_parallel_initialized() -> bool:
 def destroy_parallel() -> None:
     global _CONTEXT, _OWNS_PROCESS_GROUP
     _CONTEXT = None
+    if dist.is_initialized():
+        # peer-mapped buffers go first, while the groups that own them still exist
+        from ..distributed import symmetric
+        symmetric.close_all()
     if _OWNS_PROCESS_GROUP and dist.is_initialized():
         dist.destroy_process_group()
     _OWNS_PROCESS_GROUP = False
