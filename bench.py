@@ -196,6 +196,12 @@ def main() -> int:
         dist.barrier()
         torch.cuda.synchronize()
 
+    # Set-up, not warm-up: the trainer runs a few eager steps and then captures
+    # the step into a CUDA graph; do that before the W warm-up steps so that the
+    # timed region never contains the capture, whatever W is.
+    runner.prepare(ids_dev[0])
+    barrier()
+
     # ---- device-timed region: inputs already resident ----
     for i in range(args.warmup):
         runner.step_device(ids_dev[i % 4])
@@ -352,6 +358,15 @@ class B200Runner:
         self.graphed = self.trainer.graphed
         return loss
 
+    def prepare(self, ids_dev) -> None:
+        if self.trainer is None:
+            return
+        for _ in range(6):
+            if self.trainer.graphed or self.trainer.graph_error or self.args.no_graph:
+                break
+            self.trainer.step(ids_dev)
+        self.graphed = self.trainer.graphed
+
     def step_host(self, ids_pinned):
         import torch
         if self.trainer is None:
@@ -441,6 +456,9 @@ class ReferenceRunner:
         return 0.0
 
     def check(self) -> None:
+        pass
+
+    def prepare(self, ids_dev) -> None:
         pass
 
     def close(self) -> None:

@@ -411,11 +411,16 @@ __global__ void col_reduce_stage1(const __nv_bfloat16* __restrict__ dy, const __
 // column group g; the last block of a column group to finish adds the S
 // partial rows with float4 loads (4 x 64 threads, one quarter of the splits
 // each) and stores / accumulates the bf16 result.
-__global__ void __launch_bounds__(256)
+// MODE is a template parameter so that the plain column sum (bias gradients,
+// the common case) does not carry the registers of the dgamma / dbeta form and
+// keeps four blocks per SM.
+template <int MODE>
+__global__ void __launch_bounds__(256, MODE == 0 ? 4 : 2)
 col_reduce_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                       const float* __restrict__ mean_in, const float* __restrict__ rstd_in, float* partial,
-                      int rows, int H, int ld, int mode, int rms, __nv_bfloat16* out0, __nv_bfloat16* out1,
+                      int rows, int H, int ld, int rms, __nv_bfloat16* out0, __nv_bfloat16* out1,
                       int accumulate) {
+  constexpr int mode = MODE;
   __shared__ __align__(16) float red[2][8][256];
   __shared__ int is_last;
   const int lane = threadIdx.x & 31;
@@ -693,9 +698,14 @@ extern "C" int nmb_col_reduce(const void* dy, int ld, const void* x, const float
     int split = 8;  // at least two blocks per SM, at most kColSplit partial rows
     while (split < kColSplit && groups * split < 2 * sm_count()) split *= 2;
     while (split > 1 && split * 8 > rows) split /= 2;
-    col_reduce_vec_kernel<<<dim3(groups, split), 256, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows, H, ld,
-        mode, rms, static_cast<__nv_bfloat16*>(out0), static_cast<__nv_bfloat16*>(out1), accumulate);
+    if (mode == 1)
+      col_reduce_vec_kernel<1><<<dim3(groups, split), 256, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows, H,
+          ld, rms, static_cast<__nv_bfloat16*>(out0), static_cast<__nv_bfloat16*>(out1), accumulate);
+    else
+      col_reduce_vec_kernel<0><<<dim3(groups, split), 256, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows, H,
+          ld, rms, static_cast<__nv_bfloat16*>(out0), static_cast<__nv_bfloat16*>(out1), accumulate);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : 400 + e;
   }
