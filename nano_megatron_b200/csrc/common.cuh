@@ -152,6 +152,83 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, ui
       : "memory");
 }
 
+// ------------------------------------------------- CTA pairs (cta_group::2) --
+// Two CTAs of a cluster share one MMA: each keeps its own 128 rows of A and its
+// half of B in its own shared memory (same offsets in both), the even CTA
+// issues, each CTA's TMEM receives its 128 rows of D.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `p` (a shared-memory pointer of this CTA) in CTA `cta` of the cluster
+__device__ __forceinline__ uint32_t cluster_addr(const void* p, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
+  // Default (CTA-scope release) semantics: the explicit `.release.cluster` form
+  // measured ~1200 clocks per arrival (it fences all earlier writes cluster-wide);
+  // what these arrivals publish is async-proxy data already tracked by barriers.
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
+// Non-blocking test: a thread suspended in try_wait was seen to sleep out its
+// time limit when the arrival comes from another CTA, which cost about a
+// microsecond per wait.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on a barrier that other CTAs of the cluster arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* status, int where) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > kWaitBudgetCycles) {
+        report_status(status, kMbarTimeout, where);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// One arrival on the barrier at shared::cluster address `cluster_bar_addr` (own
+// or peer CTA) once every pair-MMA issued so far by this thread has completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar_addr)
+               : "memory");
+}
+// D[tmem of both CTAs] (+)= A[256 x 16, 128 rows per CTA] * B[N x 16, N/2 rows per CTA]
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle.  `lbo`/`sbo` in bytes.
 //   K-major operand  : rows of 128 B (64 bf16 along K); sbo = 1024 (8 rows), lbo unused.
 //   MN-major operand : rows of 128 B (64 bf16 along M/N), one row per K index;

@@ -260,6 +260,160 @@ __device__ void reduce_phase(const FusedComm& fc, int n_ctas, int N, int* status
   }
 }
 
+// Epilogue of one 128-row accumulator tile for one warp: drains its half of
+// the BN columns of TMEM lane quadrant `t_row` (32 columns at a time), applies
+// alpha / bias / GELU / dGELU / residual / accumulate and stores row `row`.
+template <int BN>
+__device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const FusedComm& fc, uint32_t t_row, int row,
+                                                 bool row_ok, int n0, int half, int N) {
+#pragma unroll 1
+  for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+    const int col0 = n0 + c * 32;
+    if (col0 >= N) break;  // uniform across the warp
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c * 32, r);
+    tmem_ld_wait();
+    if (!row_ok) continue;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
+    const bool full_chunk = (col0 + 32 <= N);
+    if (full_chunk) {
+      if (ep.bias != nullptr) {
+        const uint4* bp = reinterpret_cast<const uint4*>(ep.bias + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 u = __ldg(bp + q);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 f = unpack_bf16x2(w[t]);
+            v[q * 8 + t * 2] += f.x;
+            v[q * 8 + t * 2 + 1] += f.y;
+          }
+        }
+      }
+      if (ep.mode == kEpiGelu) {
+        uint4* ap = reinterpret_cast<uint4*>(ep.aux_out + static_cast<size_t>(row) * ep.ld_aux + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 u;
+          u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+          u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+          u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+          u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+          ap[q] = u;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          // GELU of the value the backward pass will see (bf16-rounded).
+          const float h = __bfloat162float(__float2bfloat16(v[j]));
+          v[j] = gelu_erf_f(h);
+        }
+      } else if (ep.mode == kEpiDGelu) {
+        const uint4* ap =
+            reinterpret_cast<const uint4*>(ep.aux_in + static_cast<size_t>(row) * ep.ld_aux + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 u = ap[q];
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 f = unpack_bf16x2(w[t]);
+            v[q * 8 + t * 2] *= gelu_erf_grad_f(f.x);
+            v[q * 8 + t * 2 + 1] *= gelu_erf_grad_f(f.y);
+          }
+        }
+      }
+      if (ep.residual != nullptr) {
+        const uint4* rp =
+            reinterpret_cast<const uint4*>(ep.residual + static_cast<size_t>(row) * ep.ldr + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 u = rp[q];
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 f = unpack_bf16x2(w[t]);
+            v[q * 8 + t * 2] += f.x;
+            v[q * 8 + t * 2 + 1] += f.y;
+          }
+        }
+      }
+      if (ep.out_f32) {
+        float4* cp = reinterpret_cast<float4*>(static_cast<float*>(ep.c) +
+                                               static_cast<size_t>(row) * ep.ldc + col0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          if (ep.accumulate) {
+            const float4 old = cp[q];
+            o.x += old.x;
+            o.y += old.y;
+            o.z += old.z;
+            o.w += old.w;
+          }
+          cp[q] = o;
+        }
+      } else {
+        __nv_bfloat16* c_row = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc;
+        if (fc.rs_mode != 0) {
+          // partial tile -> slot [my rank] of the owner's staging buffer
+          const int owner = row_owner(fc, row);
+          c_row = static_cast<__nv_bfloat16*>(fc.rs_stage[owner]) +
+                  (static_cast<size_t>(fc.rank) * fc.rows_per_rank + row_local(fc, row)) * N;
+        }
+        uint4* cp = reinterpret_cast<uint4*>(c_row + col0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (ep.accumulate) {
+            const uint4 u = cp[q];
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float2 f = unpack_bf16x2(w[t]);
+              v[q * 8 + t * 2] += f.x;
+              v[q * 8 + t * 2 + 1] += f.y;
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+          o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+          o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+          o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+          cp[q] = o;
+        }
+      }
+    } else {
+      // Ragged last chunk of the N dimension: scalar path.
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = col0 + j;
+        if (col >= N) continue;
+        float x = v[j];
+        if (ep.bias != nullptr) x += __bfloat162float(ep.bias[col]);
+        if (ep.mode == kEpiGelu) {
+          const __nv_bfloat16 hb = __float2bfloat16(x);
+          ep.aux_out[static_cast<size_t>(row) * ep.ld_aux + col] = hb;
+          x = gelu_erf_f(__bfloat162float(hb));
+        } else if (ep.mode == kEpiDGelu) {
+          x *= gelu_erf_grad_f(__bfloat162float(ep.aux_in[static_cast<size_t>(row) * ep.ld_aux + col]));
+        }
+        if (ep.residual != nullptr)
+          x += __bfloat162float(ep.residual[static_cast<size_t>(row) * ep.ldr + col]);
+        if (ep.out_f32) {
+          float* cp = static_cast<float*>(ep.c) + static_cast<size_t>(row) * ep.ldc + col;
+          *cp = ep.accumulate ? (*cp + x) : x;
+        } else {
+          __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc + col;
+          if (ep.accumulate) x += __bfloat162float(*cp);
+          *cp = __float2bfloat16(x);
+        }
+      }
+    }
+  }
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -446,152 +600,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
-        tmem_ld_wait();
-        if (!row_ok) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
-        const bool full_chunk = (col0 + 32 <= N);
-        if (full_chunk) {
-          if (ep.bias != nullptr) {
-            const uint4* bp = reinterpret_cast<const uint4*>(ep.bias + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 u = __ldg(bp + q);
-              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                const float2 f = unpack_bf16x2(w[t]);
-                v[q * 8 + t * 2] += f.x;
-                v[q * 8 + t * 2 + 1] += f.y;
-              }
-            }
-          }
-          if (ep.mode == kEpiGelu) {
-            uint4* ap = reinterpret_cast<uint4*>(ep.aux_out + static_cast<size_t>(row) * ep.ld_aux + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 u;
-              u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-              u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-              u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-              u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-              ap[q] = u;
-            }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              // GELU of the value the backward pass will see (bf16-rounded).
-              const float h = __bfloat162float(__float2bfloat16(v[j]));
-              v[j] = gelu_erf_f(h);
-            }
-          } else if (ep.mode == kEpiDGelu) {
-            const uint4* ap =
-                reinterpret_cast<const uint4*>(ep.aux_in + static_cast<size_t>(row) * ep.ld_aux + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 u = ap[q];
-              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                const float2 f = unpack_bf16x2(w[t]);
-                v[q * 8 + t * 2] *= gelu_erf_grad_f(f.x);
-                v[q * 8 + t * 2 + 1] *= gelu_erf_grad_f(f.y);
-              }
-            }
-          }
-          if (ep.residual != nullptr) {
-            const uint4* rp =
-                reinterpret_cast<const uint4*>(ep.residual + static_cast<size_t>(row) * ep.ldr + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 u = rp[q];
-              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                const float2 f = unpack_bf16x2(w[t]);
-                v[q * 8 + t * 2] += f.x;
-                v[q * 8 + t * 2 + 1] += f.y;
-              }
-            }
-          }
-          if (ep.out_f32) {
-            float4* cp = reinterpret_cast<float4*>(static_cast<float*>(ep.c) +
-                                                   static_cast<size_t>(row) * ep.ldc + col0);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-              if (ep.accumulate) {
-                const float4 old = cp[q];
-                o.x += old.x;
-                o.y += old.y;
-                o.z += old.z;
-                o.w += old.w;
-              }
-              cp[q] = o;
-            }
-          } else {
-            __nv_bfloat16* c_row = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc;
-            if (fc.rs_mode != 0) {
-              // partial tile -> slot [my rank] of the owner's staging buffer
-              const int owner = row_owner(fc, row);
-              c_row = static_cast<__nv_bfloat16*>(fc.rs_stage[owner]) +
-                      (static_cast<size_t>(fc.rank) * fc.rows_per_rank + row_local(fc, row)) * N;
-            }
-            uint4* cp = reinterpret_cast<uint4*>(c_row + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (ep.accumulate) {
-                const uint4 u = cp[q];
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                  const float2 f = unpack_bf16x2(w[t]);
-                  v[q * 8 + t * 2] += f.x;
-                  v[q * 8 + t * 2 + 1] += f.y;
-                }
-              }
-              uint4 o;
-              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-              cp[q] = o;
-            }
-          }
-        } else {
-          // Ragged last chunk of the N dimension: scalar path.
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = col0 + j;
-            if (col >= N) continue;
-            float x = v[j];
-            if (ep.bias != nullptr) x += __bfloat162float(ep.bias[col]);
-            if (ep.mode == kEpiGelu) {
-              const __nv_bfloat16 hb = __float2bfloat16(x);
-              ep.aux_out[static_cast<size_t>(row) * ep.ld_aux + col] = hb;
-              x = gelu_erf_f(__bfloat162float(hb));
-            } else if (ep.mode == kEpiDGelu) {
-              x *= gelu_erf_grad_f(__bfloat162float(ep.aux_in[static_cast<size_t>(row) * ep.ld_aux + col]));
-            }
-            if (ep.residual != nullptr)
-              x += __bfloat162float(ep.residual[static_cast<size_t>(row) * ep.ldr + col]);
-            if (ep.out_f32) {
-              float* cp = static_cast<float*>(ep.c) + static_cast<size_t>(row) * ep.ldc + col;
-              *cp = ep.accumulate ? (*cp + x) : x;
-            } else {
-              __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc + col;
-              if (ep.accumulate) x += __bfloat162float(*cp);
-              *cp = __float2bfloat16(x);
-            }
-          }
-        }
-      }
+      epilogue_columns<BN>(ep, fc, t_row, row, row_ok, n0, half, N);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -610,6 +619,314 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (fc.rs_mode != 0 && *abort_flag == 0) reduce_phase(fc, n_gemm_ctas, N, status);
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant (tcgen05.mma.cta_group::2): a cluster of two CTAs computes a
+// 256 x 256 tile.  Each CTA loads its own 128 rows of A and its own 128 rows
+// (half) of B, so a k-block costs 32 KB of shared-memory fill and operand reads
+// per CTA instead of 48 KB for the same 128 x 256 of output, which is what
+// bounds the single-CTA kernel.  No multicast load: the halves differ.
+//
+//   warp 0      TMA producer (both CTAs, own barriers)
+//   warp 1      even CTA: MMA issuer for the pair; odd CTA: relay that forwards
+//               "my stage is full" to the even CTA's peer_full barrier
+//   warps 2..9  epilogue (both CTAs, own 128 rows of D)
+// The issuer commits to the even CTA's empty / acc_full barriers; that CTA's
+// producer / first epilogue warp forward those signals to the odd CTA, whose
+// epilogue warps in turn arrive on the even CTA's acc_empty barriers.
+// Optional cycle accounting of the roles of pair 0 (built only with
+// -DNMB_GEMM_PROF; the counters go to the buffer passed as `aux_in` of a plain
+// epilogue): where each role's time goes between waiting and working.
+#ifdef NMB_GEMM_PROF
+#define GP_DECL long long gp_t = clock64(); long long gp_acc[4] = {0, 0, 0, 0}; \
+  long long* gp_out = (pair == 0 && ep.mode == kEpiPlain) ? reinterpret_cast<long long*>(const_cast<__nv_bfloat16*>(ep.aux_in)) : nullptr;
+#define GP_LAP(k) do { const long long t = clock64(); gp_acc[k] += t - gp_t; gp_t = t; } while (0)
+#define GP_STORE(base) do { if (gp_out != nullptr) for (int k = 0; k < 4; ++k) gp_out[(base) + k] = gp_acc[k]; } while (0)
+#else
+#define GP_DECL
+#define GP_LAP(k)
+#define GP_STORE(base)
+#endif
+
+struct GemmPairSmem {
+  static constexpr int kStages = 6;
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = 128 * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  // full, empty, peer_full [kStages]; acc_full[2], acc_empty[2]; tmem slot, abort
+  static constexpr int kTotal = kBarOffset + (3 * kStages + 4) * 8 + 16;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 GemmEpilogue ep, const __grid_constant__ FusedComm fc, int M, int N, int K, int* status) {
+  using L = GemmPairSmem;
+  constexpr int BN = 256;
+  constexpr int STAGES = L::kStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* peer_full = empty_bar + STAGES;
+  uint64_t* acc_full = peer_full + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();
+  const bool leader = cta == 0;
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+  const int tiles_m = (M + 255) / 256;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + kBK - 1) / kBK;
+  constexpr uint32_t kTmemCols = 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+      mbar_init(&peer_full[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 16);  // 8 epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);  // the whole TMEM: base 0 in both CTAs
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int fills = 0;
+      GP_DECL
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        const int m0 = (tile % tiles_m) * 256 + static_cast<int>(cta) * 128;
+        const int nb0 = (tile / tiles_m) * BN + static_cast<int>(cta) * 128;
+        for (int kb = 0; kb < num_kb; ++kb, ++fills) {
+          if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1, abort_flag, status, 11)) {
+            ok = false;
+            break;
+          }
+          // The issuer commits to the even CTA's barrier only; pass a real
+          // release (not the free first lap of the ring) on to the odd CTA.
+          GP_LAP(0);  // waited for an empty stage
+          if (leader && fills >= STAGES) mbar_arrive_cluster(cluster_addr(&empty_bar[stage], 1));
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          if (!A_MN) {
+            tma_load_2d(sa, &tma_a, &full_bar[stage], kb * kBK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d(sa + c * 8192, &tma_a, &full_bar[stage], m0 + c * 64, kb * kBK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * kBK, nb0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d(sb + c * 8192, &tma_b, &full_bar[stage], nb0 + c * 64, kb * kBK);
+          }
+          GP_LAP(1);  // issued the loads
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      GP_STORE(leader ? 0 : 4);
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ---------------------------------------------- MMA issuer of the pair --
+      constexpr uint32_t idesc = make_idesc_bf16(256, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      GP_DECL
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++local) {
+        const int buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait_cluster(&acc_empty[buf], acc_phase ^ 1, abort_flag, status, 12)) break;
+        tc_fence_after();
+        GP_LAP(0);  // waited for a free accumulator
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, 13)) {
+            ok = false;
+            break;
+          }
+          GP_LAP(1);  // waited for this CTA's loads
+          if (!mbar_wait_cluster(&peer_full[stage], phase, abort_flag, status, 14)) {
+            ok = false;
+            break;
+          }
+          GP_LAP(2);  // waited for the odd CTA's loads
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, 8192, 1024)
+                                     : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024)
+                                     : make_smem_desc(sb + k * 32, 16, 1024);
+            tc_mma_bf16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // the stage may be refilled once these MMAs have read it (the even
+          // CTA's producer forwards the release to the odd CTA)
+          tc_commit_pair(smem_u32(&empty_bar[stage]));
+          GP_LAP(3);  // issued MMAs + commit
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit_pair(smem_u32(&acc_full[buf]));  // forwarded to the odd CTA by epilogue warp 2
+      }
+      GP_STORE(8);
+    } else if (lane == 0) {
+      // ------------------------------------------ relay of the odd CTA's loads --
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      GP_DECL
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, 15)) {
+            ok = false;
+            break;
+          }
+          GP_LAP(0);  // waited for the odd CTA's loads
+          mbar_arrive_cluster(cluster_addr(&peer_full[stage], 0));
+          GP_LAP(1);  // forwarded
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      GP_STORE(12);
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue --
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    int local = 0;
+    for (int tile = pair; tile < num_tiles; tile += n_pairs, ++local) {
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int m0 = (tile % tiles_m) * 256 + static_cast<int>(cta) * 128;
+      const int n0 = (tile / tiles_m) * BN;
+      if (!mbar_wait_cluster(&acc_full[buf], acc_phase, abort_flag, status, 16)) break;
+      if (leader && warp == 2 && lane == 0) mbar_arrive_cluster(cluster_addr(&acc_full[buf], 1));
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < M;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+      epilogue_columns<BN>(ep, fc, t_row, row, row_ok, n0, half, N);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[buf], 0));
+    }
+  }
+
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody signals a CTA that has left, nobody's operands vanish under the issuer
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+static int g_pair_enabled = 1;
+static int g_pair_clusters[2][2] = {{0, 0}, {0, 0}};  // co-resident clusters per variant (0 = not asked yet)
+
+template <bool A_MN, bool B_MN>
+static int launch_gemm_pair(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep,
+                            const FusedComm& fc, int M, int N, int K, int* status, cudaStream_t stream) {
+  using L = GemmPairSmem;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!A_MN) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
+    const uint32_t box[2] = {kBK, kBM};
+    rc = make_tmap_bf16(&ta, A, 2, dims, strides, box);
+  } else {
+    const uint64_t dims[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
+    const uint32_t box[2] = {64, kBK};
+    rc = make_tmap_bf16(&ta, A, 2, dims, strides, box);
+  }
+  if (rc != 0) return 100 + rc;
+  if (!B_MN) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
+    const uint32_t box[2] = {kBK, 128};
+    rc = make_tmap_bf16(&tb, B, 2, dims, strides, box);
+  } else {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
+    const uint32_t box[2] = {64, kBK};
+    rc = make_tmap_bf16(&tb, B, 2, dims, strides, box);
+  }
+  if (rc != 0) return 200 + rc;
+
+  auto kern = gemm_pair_kernel<A_MN, B_MN>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = L::kTotal + 1024;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int& resident = g_pair_clusters[A_MN][B_MN];
+  if (resident == 0) {
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      n = sm_count() / 2 - 2;
+    }
+    resident = n;
+  }
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  const int pairs = tiles < resident ? tiles : resident;
+  cfg.gridDim = dim3(2 * pairs);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, ep, fc, M, N, K, status);
+  return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
@@ -660,6 +977,11 @@ static int launch_gemm(const void* A, int lda, const void* B, int ldb, const Gem
 template <bool A_MN, bool B_MN>
 static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
                          int M, int N, int K, int* status, cudaStream_t stream) {
+  if (g_pair_enabled && fc.ag_copy_ctas == 0 && fc.rs_mode == 0 && N >= 256) {
+    const int pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    if (pair_tiles * 3 >= sm_count() / 2)
+      return launch_gemm_pair<A_MN, B_MN>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
+  }
   const int tiles256 = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
   // A 128 x 128 UMMA reads 8 KiB of operands from shared memory per 64 clocks,
   // i.e. the full 128 B/clk of the SM, and the TMA writes compete for the same
@@ -686,6 +1008,16 @@ static int configure_gemm() {
   return e == cudaSuccess ? 0 : 300 + static_cast<int>(e);
 }
 
+template <bool A_MN, bool B_MN>
+static int configure_gemm_pair() {
+  cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       GemmPairSmem::kTotal + 1024);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(gemm_pair_kernel<A_MN, B_MN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+  return e == cudaSuccess ? 0 : 300 + static_cast<int>(e);
+}
+
 }  // namespace nmb
 
 // Opt every GEMM variant in to its dynamic shared memory size on the current
@@ -702,7 +1034,19 @@ extern "C" int nmb_gemm_configure() {
   rc |= configure_gemm<128, 6, false, true>();
   rc |= configure_gemm<128, 6, true, true>();
   rc |= configure_gemm<128, 6, true, false>();
+  rc |= configure_gemm_pair<false, false>();
+  rc |= configure_gemm_pair<false, true>();
+  rc |= configure_gemm_pair<true, true>();
+  rc |= configure_gemm_pair<true, false>();
   return rc;
+}
+
+// Route eligible GEMMs (no fused collective, N >= 256, enough tiles) to the
+// CTA-pair kernel.  Returns the previous setting.
+extern "C" int nmb_gemm_set_pair(int enabled) {
+  const int prev = nmb::g_pair_enabled;
+  nmb::g_pair_enabled = enabled ? 1 : 0;
+  return prev;
 }
 
 // C[M,N] = epilogue(alpha * A B^T).  `a_mn` / `b_mn` say that the operand is

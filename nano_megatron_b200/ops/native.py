@@ -8,6 +8,7 @@ without a device the library is simply not needed.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 from typing import Optional
@@ -65,6 +66,9 @@ def lib() -> ctypes.CDLL:
                         "(the CUDA ops do not fall back to PyTorch on a GPU)"
                     )
                 _lib = ctypes.CDLL(str(_LIB_PATH))
+                pair = os.environ.get("NMB_GEMM_PAIR")
+                if pair is not None:
+                    _lib.nmb_gemm_set_pair(int(pair != "0"))
     _configure_current_device(_lib)
     return _lib
 
