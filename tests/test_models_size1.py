@@ -157,3 +157,41 @@ def test_1f1b_pp1_equals_full_batch(ctx):
         forward_backward_1f1b(stage=stage, ctx=ctx, input_ids=ids, labels=ids, num_microbatches=3)
     with pytest.raises(ValueError):
         forward_backward_1f1b(stage=stage, ctx=ctx, input_ids=ids, labels=ids[:, :8], num_microbatches=2)
+
+
+def test_norm_with_residual_and_packed_split_cpu_paths():
+    """The fused entry points have plain-PyTorch forms on CPU with the same
+    values and gradients as the unfused expressions."""
+    import torch
+    import torch.nn.functional as F
+
+    from nano_megatron_b200.ops import functional as OF
+    from nano_megatron_b200.ops.attention import split_packed_qkv
+
+    torch.manual_seed(0)
+    x = torch.randn(3, 5, 16, requires_grad=True)
+    w, b = torch.randn(16, requires_grad=True), torch.randn(16, requires_grad=True)
+    y, xr = OF.norm_with_residual(x, w, b, 1e-5, False)
+    (y.sin() + xr).sum().backward()
+    x2 = x.detach().clone().requires_grad_(True)
+    w2, b2 = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    (F.layer_norm(x2, (16,), w2, b2, 1e-5).sin() + x2).sum().backward()
+    assert torch.allclose(x.grad, x2.grad, atol=1e-6) and torch.allclose(w.grad, w2.grad, atol=1e-6)
+    yr, _ = OF.norm_with_residual(x.detach(), w.detach(), None, 1e-5, True)
+    from nano_megatron_b200.reference.layers import rms_norm
+    assert torch.allclose(yr, rms_norm(x.detach(), w.detach(), 1e-5))
+
+    hq, hkv, d = 4, 2, 8
+    qkv = torch.randn(2, 7, (hq + 2 * hkv) * d, requires_grad=True)
+    q, k, v = split_packed_qkv(qkv, hq, hkv, d)
+    assert q.shape == (2, 7, hq, d) and k.shape == (2, 7, hkv, d) and v.shape == (2, 7, hkv, d)
+    (q.sum() * 2 + k.sum() * 3 + v.sum() * 5).backward()
+    expect = torch.cat([torch.full((hq * d,), 2.0), torch.full((hkv * d,), 3.0), torch.full((hkv * d,), 5.0)])
+    assert torch.equal(qkv.grad, expect.expand(2, 7, -1))
+
+
+def test_destroy_parallel_without_symmetric_workspaces_is_a_noop():
+    from nano_megatron_b200.distributed import symmetric
+
+    symmetric.close_all()
+    assert symmetric.workspace_for(object()) is None
