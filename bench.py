@@ -41,7 +41,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "nccl-baseline", "reference"],
+                    help="b200: this framework; nccl-baseline: this framework's modules on plain NCCL collectives "
+                         "(same as --no-symm); reference: the unmodified reference package")
     ap.add_argument("--mode", default="dp", choices=["dp", "tp", "cp", "pp"])
     ap.add_argument("--model", default="345m", choices=["345m", "760m", "1.3b", "small"])
     ap.add_argument("--batch", type=int, default=None, help="per data-parallel rank")
@@ -142,6 +144,8 @@ def emit(payload: dict) -> None:
 # ------------------------------------------------------------------------ main --
 def main() -> int:
     args = parse_args()
+    if args.impl == "nccl-baseline":
+        args.no_symm = True
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -23,6 +23,7 @@ from torch import Tensor, nn
 
 from ..distributed.ddp import DistributedDataParallel
 from ..ops import native
+from ..utils.tracing import nvtx_range
 from ..reference.optimizer import AdamW
 
 
@@ -78,12 +79,17 @@ class Trainer:
 
     # ------------------------------------------------------------------ step --
     def _step_body(self) -> Tensor:
-        self.ddp.zero_grad()
-        logits = self.ddp(self._ids)
-        loss = self._loss_fn(logits, self._labels)
-        loss.backward()
-        self.ddp.finish_grad_sync()
-        self.optimizer.step()
+        with nvtx_range("zero_grad"):
+            self.ddp.zero_grad()
+        with nvtx_range("forward"):
+            logits = self.ddp(self._ids)
+            loss = self._loss_fn(logits, self._labels)
+        with nvtx_range("backward"):
+            loss.backward()
+        with nvtx_range("grad_sync"):
+            self.ddp.finish_grad_sync()
+        with nvtx_range("optimizer"):
+            self.optimizer.step()
         return loss.detach()
 
     def _load(self, input_ids: Tensor, labels: Optional[Tensor]) -> None:

@@ -28,6 +28,7 @@ from torch import Tensor
 from . import kernels, native
 from .functional import _deliver_grad
 from .gemm import EPI_DGELU, EPI_GELU, EPI_PLAIN, gemm_bf16
+from ..utils.tracing import nvtx_range
 
 _MAX = 8
 COPY_CTAS = 16
@@ -35,7 +36,7 @@ COPY_CTAS = 16
 #: a call site's gathered-input buffer is reused by every microbatch in flight)
 ENABLED = False
 #: launches of the two fused kernels by this process (tests assert on it)
-STATS = {"allgather_gemm": 0, "gemm_reduce_scatter": 0}
+STATS = {"allgather_gemm": 0, "gemm_reduce_scatter": 0, "nvlink_bytes": 0}
 
 
 class _FusedComm(ctypes.Structure):
@@ -138,8 +139,11 @@ class TPFused:
         fc.rs_out[self.ws.rank] = out.data_ptr()
         fc.rs_bias = bias.data_ptr() if bias is not None else None
         fc.rs_residual = residual.data_ptr() if residual is not None else None
-        self._launch(a, b, b_mn, None, m, n, k, None, None, EPI_PLAIN, fc)
+        with nvtx_range("gemm_reduce_scatter"):
+            self._launch(a, b, b_mn, None, m, n, k, None, None, EPI_PLAIN, fc)
         STATS["gemm_reduce_scatter"] += 1
+        # bytes this rank stores into peers' staging slots (its partial rows they own)
+        STATS["nvlink_bytes"] += m * n * 2 * (self.ws.size - 1) // self.ws.size
         return out
 
     def allgather_gemm(self, full: Tensor, b: Tensor, seq_len: int, *, b_mn: bool = False,
@@ -156,8 +160,11 @@ class TPFused:
         fc.ag_ready = self.ready.data_ptr()
         for i, p in enumerate(self.ws.peers_of(full)):
             fc.ag_src[i] = p
-        self._launch(full, b, b_mn, out, m, n, k, bias, aux_out, mode, fc)
+        with nvtx_range("allgather_gemm"):
+            self._launch(full, b, b_mn, out, m, n, k, bias, aux_out, mode, fc)
         STATS["allgather_gemm"] += 1
+        # bytes the copy CTAs pull from the peers' shards
+        STATS["nvlink_bytes"] += m * k * 2 * (self.ws.size - 1) // self.ws.size
         return out
 
 

@@ -199,3 +199,20 @@ def test_cli_reproduces_the_documented_oracle_losses(capsys):
 if __name__ == "__main__":
     from tests._dist_utils import run_worker_if_requested
     run_worker_if_requested(globals())
+
+
+def test_nvtx_ranges_are_inert_without_cuda_and_toggle():
+    from nano_megatron_b200.utils import tracing
+
+    was = tracing.enabled()
+    try:
+        tracing.enable(True)
+        assert tracing.enabled()
+        with tracing.nvtx_range("phase"):   # no CUDA here: must not raise
+            pass
+        tracing.enable(False)
+        assert not tracing.enabled()
+        with tracing.nvtx_range("phase"):
+            pass
+    finally:
+        tracing.enable(was)
