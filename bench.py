@@ -44,7 +44,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--impl", default="b200", choices=["b200", "nccl-baseline", "reference"],
                     help="b200: this framework; nccl-baseline: this framework's modules on plain NCCL collectives "
                          "(same as --no-symm); reference: the unmodified reference package")
-    ap.add_argument("--mode", default="dp", choices=["dp", "tp", "cp", "pp"])
+    ap.add_argument("--mode", default="dp", choices=["dp", "tp", "cp", "pp", "composite"],
+                    help="composite = pp: TP2 x PP2 (x DP2 at 8 GPUs) with the 1F1B schedule")
     ap.add_argument("--model", default="345m", choices=["345m", "760m", "1.3b", "small"])
     ap.add_argument("--batch", type=int, default=None, help="per data-parallel rank")
     ap.add_argument("--seq", type=int, default=None)
@@ -146,6 +147,8 @@ def main() -> int:
     args = parse_args()
     if args.impl == "nccl-baseline":
         args.no_symm = True
+    if args.mode == "composite":
+        args.mode = "pp"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -84,6 +84,16 @@ def test_resume_reproduces_the_trajectory_bit_for_bit(ctx, tmp_path):
     ref = ReferenceGPT(cfg)
     ref.load_state_dict(merged["model"])                      # loads into the oracle unchanged
 
+    # the command-line merge writes the same thing as one portable file
+    from nano_megatron_b200.cli import merge_checkpoint as merge_cli
+    from nano_megatron_b200.reference import ReferenceGPTConfig
+    out = str(tmp_path / "merged.pt")
+    assert merge_cli.main([str(tmp_path), out]) == 0
+    blob = torch.load(out, map_location="cpu", weights_only=False)
+    again = ReferenceGPT(ReferenceGPTConfig(**blob["config"]))
+    again.load_state_dict(blob["model"])
+    assert blob["step"] == 2 and set(blob["optimizer"]) == set(merged["optimizer"])
+
 
 @pytest.mark.parametrize("knobs", [dict(), dict(gated_linear_unit=True, num_query_groups=2)])
 def test_shard_rules_round_trip(knobs):
