@@ -30,6 +30,10 @@ CHANNEL_TP, CHANNEL_DP, CHANNEL_CP, CHANNEL_AUX = 0, 1, 2, 3
 # with that many blocks (it shares SMs with the backward GEMMs instead of taking
 # them over); positive: the latency-first kernel.
 DDP_ALLREDUCE_BLOCKS = int(os.environ.get("NMB_DDP_AR_BLOCKS", "-148"))
+# Optional arena: with NMB_SYMM_ARENA_MB=<n> tensors up to n MiB are carved out
+# of shared n-MiB symmetric allocations (one IPC handle and one handle exchange
+# per arena instead of per tensor).  Off (0) by default.
+ARENA_BYTES = int(os.environ.get("NMB_SYMM_ARENA_MB", "0")) << 20
 
 
 class _RawCuda:
@@ -65,6 +69,8 @@ class SymmetricWorkspace:
         if self.size > self.max_ranks:
             raise RuntimeError(f"group of {self.size} ranks exceeds the kernel limit of {self.max_ranks}")
         self._closed = False
+        self._arena: Optional[SymmetricAllocation] = None
+        self._arena_used = 0
         self._allocs: list[SymmetricAllocation] = []
         self._by_ptr: dict[int, tuple[SymmetricAllocation, int]] = {}
         self.pad = self._alloc_raw(self.channels * self.max_blocks * self.max_ranks * 4)
@@ -123,9 +129,20 @@ class SymmetricWorkspace:
     def alloc_tensor(self, numel: int, dtype: torch.dtype) -> Optional[torch.Tensor]:
         """Collective: a zero-filled 1-D tensor of ``numel`` elements in symmetric memory."""
         item = torch.empty((), dtype=dtype).element_size()
-        alloc = self._alloc_raw(numel * item)
-        t = alloc.bytes[: numel * item].view(dtype)
-        self._by_ptr[t.data_ptr()] = (alloc, 0)
+        nbytes = numel * item
+        if 0 < nbytes <= ARENA_BYTES:
+            # Every rank makes the same requests in the same order, so the offsets
+            # inside the arena agree across ranks (peers_of adds the same offset).
+            step = (nbytes + 1023) // 1024 * 1024
+            if self._arena is None or self._arena_used + step > self._arena.nbytes:
+                self._arena = self._alloc_raw(ARENA_BYTES)
+                self._arena_used = 0
+            alloc, off = self._arena, self._arena_used
+            self._arena_used += step
+        else:
+            alloc, off = self._alloc_raw(nbytes), 0
+        t = alloc.bytes[off: off + nbytes].view(dtype)
+        self._by_ptr[t.data_ptr()] = (alloc, off)
         return t
 
     def peers_of(self, t: torch.Tensor) -> list[int]:
