@@ -98,6 +98,7 @@ class SymmetricWorkspace:
             lib.nmb_symm_free(ctypes.c_void_p(alloc.local_ptr))
         self._allocs.clear()
         self._by_ptr.clear()
+        self._arena = None
 
     # ------------------------------------------------------------ allocation --
     def _alloc_raw(self, nbytes: int) -> SymmetricAllocation:
