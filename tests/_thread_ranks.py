@@ -1,0 +1,138 @@
+"""In-process multi-rank simulator for the CommBackend protocol.
+
+``run_ranks(n, fn)`` runs ``fn(rank, backend)`` on ``n`` threads; the backend
+objects share one rendezvous, so collectives exchange real data between the
+"ranks".  CPU autograd runs a backward pass on the thread that called it, so
+whole forward + backward passes of the parallel operators can be checked for
+exact arithmetic without processes or sockets.  (The socket-based Gloo tests
+cover the real transport; this covers the maths, quickly and for any rank
+count.)
+"""
+from __future__ import annotations
+
+import threading
+from typing import Any, Callable, Optional
+
+import torch
+from torch import Tensor
+
+_OPS = {
+    "sum": lambda ts: torch.stack(ts).sum(0),
+    "max": lambda ts: torch.stack(ts).max(0).values,
+    "min": lambda ts: torch.stack(ts).min(0).values,
+    "product": lambda ts: torch.stack(ts).prod(0),
+}
+
+
+class _Rendezvous:
+    def __init__(self, n: int) -> None:
+        self.n = n
+        self.barrier = threading.Barrier(n, timeout=30)
+        self.slots: list[Any] = [None] * n
+        self.mail: dict[tuple[int, int], list[Tensor]] = {}
+        self.mail_cv = threading.Condition()
+
+    def exchange(self, rank: int, item: Any) -> list[Any]:
+        """Everybody deposits one item and gets everybody's items."""
+        self.slots[rank] = item
+        self.barrier.wait()
+        items = list(self.slots)
+        self.barrier.wait()            # nobody overwrites a slot that is still being read
+        return items
+
+
+class _Done:
+    def wait(self) -> None:
+        return None
+
+
+class ThreadBackend:
+    """One per simulated rank; ``group`` arguments are ignored (one group)."""
+
+    def __init__(self, rank: int, rdv: _Rendezvous) -> None:
+        self.rank, self._rdv = rank, rdv
+        self.counts: dict[str, int] = {}
+
+    def _count(self, name: str) -> None:
+        self.counts[name] = self.counts.get(name, 0) + 1
+
+    def all_reduce(self, tensor: Tensor, *, group: Optional[Any] = None, op: str = "sum", async_op: bool = False):
+        self._count("all_reduce")
+        parts = self._rdv.exchange(self.rank, tensor.detach().clone())
+        tensor.copy_(_OPS[op](parts))
+        return _Done() if async_op else tensor
+
+    def reduce_scatter(self, output: Tensor, input_list: list[Tensor], *, group: Optional[Any] = None,
+                       op: str = "sum") -> Tensor:
+        self._count("reduce_scatter")
+        everyone = self._rdv.exchange(self.rank, [t.detach().clone() for t in input_list])
+        output.copy_(_OPS[op]([lst[self.rank] for lst in everyone]))
+        return output
+
+    def all_gather(self, tensor_list: list[Tensor], tensor: Tensor, *, group: Optional[Any] = None) -> list[Tensor]:
+        self._count("all_gather")
+        for dst, src in zip(tensor_list, self._rdv.exchange(self.rank, tensor.detach().clone())):
+            dst.copy_(src)
+        return tensor_list
+
+    def all_gather_into_tensor(self, output: Tensor, input: Tensor, *, group: Optional[Any] = None) -> Tensor:
+        self._count("all_gather_into_tensor")
+        parts = self._rdv.exchange(self.rank, input.detach().clone())
+        if output.dim() == input.dim():
+            output.copy_(torch.cat(parts, dim=0))
+        else:
+            output.copy_(torch.stack(parts, dim=0))
+        return output
+
+    def broadcast(self, tensor: Tensor, src: int, *, group: Optional[Any] = None) -> Tensor:
+        self._count("broadcast")
+        tensor.copy_(self._rdv.exchange(self.rank, tensor.detach().clone())[src])
+        return tensor
+
+    def send(self, tensor: Tensor, dst: int, *, group: Optional[Any] = None) -> None:
+        self._count("send")
+        with self._rdv.mail_cv:
+            self._rdv.mail.setdefault((self.rank, dst), []).append(tensor.detach().clone())
+            self._rdv.mail_cv.notify_all()
+
+    def recv(self, tensor: Tensor, src: int, *, group: Optional[Any] = None) -> Tensor:
+        self._count("recv")
+        key = (src, self.rank)
+        with self._rdv.mail_cv:
+            ok = self._rdv.mail_cv.wait_for(lambda: self._rdv.mail.get(key), timeout=30)
+            if not ok:
+                raise TimeoutError(f"rank {self.rank}: nothing arrived from rank {src}")
+            tensor.copy_(self._rdv.mail[key].pop(0))
+        return tensor
+
+    def barrier(self, *, group: Optional[Any] = None) -> None:
+        self._rdv.exchange(self.rank, None)
+
+
+def run_ranks(n: int, fn: Callable[[int, ThreadBackend], Any]) -> list[Any]:
+    """Run ``fn(rank, backend)`` for ``n`` simulated ranks; returns their results
+    in rank order and re-raises the first failure."""
+    rdv = _Rendezvous(n)
+    results: list[Any] = [None] * n
+    errors: list[Optional[BaseException]] = [None] * n
+
+    def body(rank: int) -> None:
+        try:
+            results[rank] = fn(rank, ThreadBackend(rank, rdv))
+        except BaseException as exc:  # noqa: BLE001 - reported to the caller below
+            errors[rank] = exc
+            rdv.barrier.abort()
+
+    threads = [threading.Thread(target=body, args=(r,), daemon=True) for r in range(n)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    real = [e for e in errors if e is not None and not isinstance(e, threading.BrokenBarrierError)]
+    if real:
+        raise real[0]
+    if any(e is not None for e in errors):
+        raise errors[[i for i, e in enumerate(errors) if e is not None][0]]
+    if any(t.is_alive() for t in threads):
+        raise TimeoutError("a simulated rank did not finish")
+    return results
