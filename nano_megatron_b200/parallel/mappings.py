@@ -243,6 +243,8 @@ class _CopyToTPRegion(torch.autograd.Function):
             buf = buffers.get_buffer(grad.shape, grad.dtype, grad.device)
             buf.copy_(grad)
             grad = buf
+        elif not grad.is_contiguous():
+            grad = grad.contiguous()   # e.g. an expanded gradient: the collective writes in place
         _wait(backend.all_reduce(grad, group=group, op="sum", async_op=True))
         return grad, None, None, None
 
