@@ -24,21 +24,46 @@ _OPS = {
 }
 
 
-class _Rendezvous:
-    def __init__(self, n: int) -> None:
-        self.n = n
-        self.barrier = threading.Barrier(n, timeout=30)
-        self.slots: list[Any] = [None] * n
-        self.mail: dict[tuple[int, int], list[Tensor]] = {}
-        self.mail_cv = threading.Condition()
+class _Meeting:
+    """Exchange point of one group of ranks."""
+
+    def __init__(self, members: tuple[int, ...]) -> None:
+        self.members = members
+        self.barrier = threading.Barrier(len(members), timeout=30)
+        self.slots: list[Any] = [None] * len(members)
 
     def exchange(self, rank: int, item: Any) -> list[Any]:
-        """Everybody deposits one item and gets everybody's items."""
-        self.slots[rank] = item
+        """Every member deposits one item and gets all members' items (member order)."""
+        self.slots[self.members.index(rank)] = item
         self.barrier.wait()
         items = list(self.slots)
         self.barrier.wait()            # nobody overwrites a slot that is still being read
         return items
+
+
+class _Rendezvous:
+    def __init__(self, n: int) -> None:
+        self.n = n
+        self._lock = threading.Lock()
+        self._meetings: dict[tuple[int, ...], _Meeting] = {}
+        self.mail: dict[tuple[int, int], list[Tensor]] = {}
+        self.mail_cv = threading.Condition()
+        self.barrier = self.meeting(None).barrier
+
+    def meeting(self, group: Any) -> _Meeting:
+        members = tuple(range(self.n)) if group is None else tuple(group)
+        with self._lock:
+            if members not in self._meetings:
+                self._meetings[members] = _Meeting(members)
+            return self._meetings[members]
+
+    def exchange(self, rank: int, item: Any, group: Any = None) -> list[Any]:
+        return self.meeting(group).exchange(rank, item)
+
+    def abort(self) -> None:
+        with self._lock:
+            for m in self._meetings.values():
+                m.barrier.abort()
 
 
 class _Done:
@@ -47,7 +72,8 @@ class _Done:
 
 
 class ThreadBackend:
-    """One per simulated rank; ``group`` arguments are ignored (one group)."""
+    """One per simulated rank.  A ``group`` is ``None`` (all ranks) or a tuple of
+    global ranks; a rank's position in the tuple is its rank in the group."""
 
     def __init__(self, rank: int, rdv: _Rendezvous) -> None:
         self.rank, self._rdv = rank, rdv
@@ -58,26 +84,27 @@ class ThreadBackend:
 
     def all_reduce(self, tensor: Tensor, *, group: Optional[Any] = None, op: str = "sum", async_op: bool = False):
         self._count("all_reduce")
-        parts = self._rdv.exchange(self.rank, tensor.detach().clone())
+        parts = self._rdv.exchange(self.rank, tensor.detach().clone(), group)
         tensor.copy_(_OPS[op](parts))
         return _Done() if async_op else tensor
 
     def reduce_scatter(self, output: Tensor, input_list: list[Tensor], *, group: Optional[Any] = None,
                        op: str = "sum") -> Tensor:
         self._count("reduce_scatter")
-        everyone = self._rdv.exchange(self.rank, [t.detach().clone() for t in input_list])
-        output.copy_(_OPS[op]([lst[self.rank] for lst in everyone]))
+        everyone = self._rdv.exchange(self.rank, [t.detach().clone() for t in input_list], group)
+        me = self.rank if group is None else tuple(group).index(self.rank)
+        output.copy_(_OPS[op]([lst[me] for lst in everyone]))
         return output
 
     def all_gather(self, tensor_list: list[Tensor], tensor: Tensor, *, group: Optional[Any] = None) -> list[Tensor]:
         self._count("all_gather")
-        for dst, src in zip(tensor_list, self._rdv.exchange(self.rank, tensor.detach().clone())):
+        for dst, src in zip(tensor_list, self._rdv.exchange(self.rank, tensor.detach().clone(), group)):
             dst.copy_(src)
         return tensor_list
 
     def all_gather_into_tensor(self, output: Tensor, input: Tensor, *, group: Optional[Any] = None) -> Tensor:
         self._count("all_gather_into_tensor")
-        parts = self._rdv.exchange(self.rank, input.detach().clone())
+        parts = self._rdv.exchange(self.rank, input.detach().clone(), group)
         if output.dim() == input.dim():
             output.copy_(torch.cat(parts, dim=0))
         else:
@@ -86,7 +113,8 @@ class ThreadBackend:
 
     def broadcast(self, tensor: Tensor, src: int, *, group: Optional[Any] = None) -> Tensor:
         self._count("broadcast")
-        tensor.copy_(self._rdv.exchange(self.rank, tensor.detach().clone())[src])
+        members = tuple(range(self._rdv.n)) if group is None else tuple(group)
+        tensor.copy_(self._rdv.exchange(self.rank, tensor.detach().clone(), group)[members.index(src)])   # src is global
         return tensor
 
     def send(self, tensor: Tensor, dst: int, *, group: Optional[Any] = None) -> None:
@@ -106,7 +134,7 @@ class ThreadBackend:
         return tensor
 
     def barrier(self, *, group: Optional[Any] = None) -> None:
-        self._rdv.exchange(self.rank, None)
+        self._rdv.exchange(self.rank, None, group)
 
 
 def run_ranks(n: int, fn: Callable[[int, ThreadBackend], Any]) -> list[Any]:
@@ -121,7 +149,7 @@ def run_ranks(n: int, fn: Callable[[int, ThreadBackend], Any]) -> list[Any]:
             results[rank] = fn(rank, ThreadBackend(rank, rdv))
         except BaseException as exc:  # noqa: BLE001 - reported to the caller below
             errors[rank] = exc
-            rdv.barrier.abort()
+            rdv.abort()
 
     threads = [threading.Thread(target=body, args=(r,), daemon=True) for r in range(n)]
     for t in threads:
@@ -136,3 +164,32 @@ def run_ranks(n: int, fn: Callable[[int, ThreadBackend], Any]) -> list[Any]:
     if any(t.is_alive() for t in threads):
         raise TimeoutError("a simulated rank did not finish")
     return results
+
+
+def thread_context(rank: int, backend: ThreadBackend, *, tp: int = 1, pp: int = 1, cp: int = 1, dp: int = 1,
+                   sequence_parallel: bool = False, order: str = "tp-cp-dp-pp"):
+    """A ``ParallelContext`` for simulated rank ``rank`` whose groups are tuples of
+    global ranks (what :class:`ThreadBackend` understands)."""
+    from nano_megatron_b200.parallel.config import ParallelConfig
+    from nano_megatron_b200.parallel.context import ParallelContext
+    from nano_megatron_b200.parallel.rank_generator import RankGenerator
+
+    gen = RankGenerator(tp=tp, dp=dp, pp=pp, cp=cp, order=order)
+    coords = gen.decode(rank)
+
+    def group_of(token: str):
+        for g in gen.get_ranks(token):
+            if rank in g:
+                return tuple(g)
+        raise AssertionError(token)
+
+    cfg = ParallelConfig(tensor_parallel_size=tp, pipeline_parallel_size=pp, context_parallel_size=cp,
+                         data_parallel_size=dp, sequence_parallel=sequence_parallel, order=order)
+    return ParallelContext(
+        config=cfg, rank=rank, world_size=gen.world_size, local_rank=rank, backend=backend,
+        tensor_parallel_size=tp, tensor_parallel_rank=coords["tp"], data_parallel_size=dp,
+        data_parallel_rank=coords["dp"], pipeline_parallel_size=pp, pipeline_parallel_rank=coords["pp"],
+        context_parallel_size=cp, context_parallel_rank=coords["cp"], tensor_parallel_group=group_of("tp"),
+        data_parallel_group=group_of("dp"), pipeline_parallel_group=group_of("pp"),
+        context_parallel_group=group_of("cp"), sequence_parallel=sequence_parallel,
+        data_context_parallel_group=group_of("dp-cp"))

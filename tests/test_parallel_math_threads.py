@@ -133,8 +133,8 @@ def test_sp_replicated_parameter_gradients_are_summed_over_ranks_once():
     def rank_fn(rank, be):
         p = torch.nn.Parameter(torch.ones(3))
         q = torch.nn.Parameter(torch.ones(2))
-        M.register_sequence_parallel_grad_allreduce(p, "G", be)
-        M.register_sequence_parallel_grad_allreduce(q, "G", be)
+        M.register_sequence_parallel_grad_allreduce(p, None, be)
+        M.register_sequence_parallel_grad_allreduce(q, None, be)
         ((p * (rank + 1)).sum() + (q * 10 * (rank + 1)).sum()).backward()
         return p.grad.clone(), q.grad.clone(), be.counts.get("all_reduce", 0)
 
