@@ -137,16 +137,24 @@ class ThreadBackend:
         self._rdv.exchange(self.rank, None, group)
 
 
-def run_ranks(n: int, fn: Callable[[int, ThreadBackend], Any]) -> list[Any]:
+def run_ranks(n: int, fn: Callable[..., Any], prepare: Optional[Callable[[int, ThreadBackend], Any]] = None) -> list[Any]:
     """Run ``fn(rank, backend)`` for ``n`` simulated ranks; returns their results
-    in rank order and re-raises the first failure."""
+    in rank order and re-raises the first failure.  With ``prepare``, the main
+    thread first calls ``prepare(rank, backend)`` for every rank in turn (the
+    place to build modules: the global random generator is shared between
+    threads) and the ranks run ``fn(rank, backend, prepared)``."""
     rdv = _Rendezvous(n)
+    backends = [ThreadBackend(r, rdv) for r in range(n)]
+    prepared = [prepare(r, backends[r]) for r in range(n)] if prepare is not None else None
     results: list[Any] = [None] * n
     errors: list[Optional[BaseException]] = [None] * n
 
     def body(rank: int) -> None:
         try:
-            results[rank] = fn(rank, ThreadBackend(rank, rdv))
+            if prepared is not None:
+                results[rank] = fn(rank, backends[rank], prepared[rank])
+            else:
+                results[rank] = fn(rank, backends[rank])
         except BaseException as exc:  # noqa: BLE001 - reported to the caller below
             errors[rank] = exc
             rdv.abort()
