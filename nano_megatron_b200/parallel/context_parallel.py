@@ -41,11 +41,12 @@ class _ScatterToContextParallelRegion(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx: Any, x: Tensor, group: Any, backend: CommBackend, cp_rank: int, cp_size: int, seq_dim: int):
-        ctx.meta = (cp_rank, cp_size, seq_dim, x.size(seq_dim) if cp_size > 1 else 0)
         if cp_size == 1:
+            ctx.meta = (cp_rank, cp_size, seq_dim, 0)
             return x
         _check(x, seq_dim)
         _check_divisible(x.size(seq_dim), cp_size)
+        ctx.meta = (cp_rank, cp_size, seq_dim, x.size(seq_dim))
         width = x.size(seq_dim) // cp_size
         return x.narrow(seq_dim, cp_rank * width, width).contiguous()
 

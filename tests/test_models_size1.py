@@ -195,3 +195,24 @@ def test_destroy_parallel_without_symmetric_workspaces_is_a_noop():
 
     symmetric.close_all()
     assert symmetric.workspace_for(object()) is None
+
+
+@pytest.mark.parametrize("name", ["gpt2", "rope_swiglu"])
+def test_trainer_on_cpu_follows_the_oracle_trajectory(ctx, name):
+    """``Trainer.step`` (zero-grad, forward, CE, backward, gradient sync, AdamW)
+    is the oracle's ``reference_train_step`` when nothing is parallel."""
+    from nano_megatron_b200.engine import Trainer
+    from nano_megatron_b200.reference import AdamW, reference_train_step
+
+    seed_all(0)
+    cfg = _cfg(**CONFIGS[name])
+    ref = ReferenceGPT(cfg)
+    ids = torch.randint(0, cfg.vocab_size, (2, 16))
+    trainer = Trainer(build_tp_gpt_from_reference(ref, ctx), ctx, lr=1e-2, weight_decay=0.01)
+    assert not trainer.graphed                               # no CUDA device: eager
+    opt = AdamW(ref.named_parameters(), lr=1e-2, weight_decay=0.01)
+    mine = [trainer.step(ids).item() for _ in range(3)]
+    want = [reference_train_step(ref, opt, ids, capture_level="minimal", step=i).loss.item() for i in range(3)]
+    assert mine == pytest.approx(want, rel=1e-6, abs=1e-6)
+    assert mine[2] < mine[0]
+    trainer.check()
