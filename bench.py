@@ -1,25 +1,40 @@
 #!/usr/bin/env python
 """Headline benchmark: GPT training tokens/sec on N GPUs of one node.
 
-    python bench.py --gpus 1 --steps 10 --warmup 3
+    python bench.py --gpus 1 --steps 100 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W [--mode dp|tp|cp|pp] [--impl reference]
 
-One step = zero-grad, forward, shifted cross entropy, backward, gradient
-synchronisation and an AdamW update, bf16 parameters, synthetic uniform token
-ids, random-init weights.  Rank 0 prints ONE JSON line.
+The headline step is zero-grad, forward, shifted cross entropy, backward,
+gradient synchronisation and an AdamW update, bf16 parameters, synthetic
+uniform token ids, random-init weights.  The same JSON line also carries
 
-``--impl reference`` runs the unmodified reference package (installed offline
-into ``baseline/_ref``) through its own modules for the same step and config.
+* ``step_without_optimizer``: the reference's own benchmark step (forward,
+  backward, gradient sync, zero-grad; nano_megatron scripts/benchmark_tp.py:182-186,
+  benchmark_dp.py:212-223), timed the same way;
+* ``peak_mem_mb``: peak device memory of the run (torch allocator peak plus
+  symmetric memory), the third column of the reference's benchmark tables;
+* ``modes`` (only when no ``--mode`` is given): the other configurations of the
+  benchmark suite at the same GPU count -- GPT-760M data parallel, GPT-345M
+  tensor + sequence parallel, GPT-1.3B context parallel, the TP x PP (x DP)
+  composite with the 1F1B schedule, and the reference's published knob set
+  (RoPE, SwiGLU, no bias, untied, vocabulary 51200) -- each with both step
+  figures.
+
+Rank 0 prints ONE JSON line.  ``--impl reference`` runs the unmodified
+reference package (installed offline into ``baseline/_ref``) through its own
+modules for the same steps and configurations.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
 import subprocess
 import sys
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -35,25 +50,37 @@ PUBLISHED = {
     ("345m", "cp", 2): 20718.0, ("760m", "cp", 2): 12422.0, ("1.3b", "cp", 2): 6420.0,
 }
 
+METRIC = "training tokens/sec/box (device-timed, max over ranks), fwd+bwd+grad-sync+AdamW, bf16"
+
 
 def parse_args() -> argparse.Namespace:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "nccl-baseline", "reference"],
                     help="b200: this framework; nccl-baseline: this framework's modules on plain NCCL collectives "
                          "(same as --no-symm); reference: the unmodified reference package")
-    ap.add_argument("--mode", default="dp", choices=["dp", "tp", "cp", "pp", "composite"],
-                    help="composite = pp: TP2 x PP2 (x DP2 at 8 GPUs) with the 1F1B schedule")
+    ap.add_argument("--mode", default=None, choices=["dp", "tp", "cp", "pp", "composite"],
+                    help="one configuration only (composite = pp: TP2 x PP2 (x DP2 at 8 GPUs) with the 1F1B "
+                         "schedule); without it the headline is dp and the other modes are added under 'modes'")
     ap.add_argument("--model", default="345m", choices=["345m", "760m", "1.3b", "small"])
+    ap.add_argument("--knobs", default="gpt2", choices=["gpt2", "published"],
+                    help="gpt2: GELU, learned positions, bias, tied, vocabulary 50304; published: the reference's "
+                         "benchmark knobs (RoPE, SwiGLU, no bias, untied, vocabulary 51200)")
     ap.add_argument("--batch", type=int, default=None, help="per data-parallel rank")
     ap.add_argument("--seq", type=int, default=None)
     ap.add_argument("--no-sp", action="store_true", help="tp mode without sequence parallelism")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--microbatches", type=int, default=4)
     ap.add_argument("--no-symm", action="store_true", help="plain NCCL collectives instead of peer-memory kernels")
-    return ap.parse_args()
+    ap.add_argument("--mode-steps", type=int, default=30, help="timed steps of each entry under 'modes'")
+    ap.add_argument("--no-modes", action="store_true", help="headline only")
+    args = ap.parse_args()
+    args.explicit_mode = args.mode is not None
+    if args.mode is None:
+        args.mode = "dp"
+    return args
 
 
 # --------------------------------------------------------------- clock sampler --
@@ -104,13 +131,18 @@ class ClockSampler:
 
 
 # -------------------------------------------------------------------- helpers --
-def model_knobs(name: str, seq: int, mode: str) -> dict:
+def model_knobs(name: str, seq: int, mode: str, knobs: str = "gpt2") -> dict:
     sizes = {"345m": (24, 1024, 16), "760m": (24, 1536, 16), "1.3b": (24, 2048, 16), "small": (4, 256, 4)}
     layers, hidden, heads = sizes[name]
-    return dict(vocab_size=50304 if name != "small" else 1024, max_seq_len=seq, hidden_size=hidden,
-                num_layers=layers, num_heads=heads, ffn_hidden_size=4 * hidden, use_bias=True,
+    base = dict(max_seq_len=seq, hidden_size=hidden, num_layers=layers, num_heads=heads,
+                ffn_hidden_size=4 * hidden, use_fused_qkv=True, attn_backend="flash")
+    if knobs == "published":
+        # nano_megatron scripts/benchmark_tp.py:94-113
+        return dict(base, vocab_size=51200 if name != "small" else 1024, use_bias=False, tie_word_embeddings=False,
+                    position_embedding_type="rope", activation_func="swiglu", gated_linear_unit=True)
+    return dict(base, vocab_size=50304 if name != "small" else 1024, use_bias=True,
                 tie_word_embeddings=(mode != "pp"), position_embedding_type="learned_absolute",
-                activation_func="gelu", gated_linear_unit=False, use_fused_qkv=True, attn_backend="flash")
+                activation_func="gelu", gated_linear_unit=False)
 
 
 def layout(args) -> dict:
@@ -128,6 +160,41 @@ def layout(args) -> dict:
     return dict(tp=1, cp=1, pp=2, dp=1, sp=False, name="pp2")
 
 
+def spec_of(args) -> dict:
+    """Workload of one configuration: layout, model knobs, batch and sequence."""
+    lay = layout(args)
+    multi_pp = args.mode == "pp" and args.gpus > 1
+    seq = args.seq or (1024 if multi_pp else 2048)
+    if args.mode == "cp" and args.gpus > 1 and args.seq is None:
+        seq = 2048 * args.gpus  # per-rank 2048 tokens, as the reference scales CP
+    batch = args.batch or (8 if multi_pp else (1 if args.model == "1.3b" else 2))
+    knobs = model_knobs(args.model, seq, args.mode if args.gpus > 1 else "dp", args.knobs)
+    return dict(lay=lay, knobs=knobs, batch=batch, seq=seq, mode=args.mode, model=args.model,
+                knob_set=args.knobs, microbatches=args.microbatches)
+
+
+def extra_specs(args) -> list[tuple[str, argparse.Namespace]]:
+    """The other configurations of the suite at this GPU count."""
+    def variant(**kw) -> argparse.Namespace:
+        ns = argparse.Namespace(**vars(args))
+        ns.batch = ns.seq = None
+        for k, v in kw.items():
+            setattr(ns, k, v)
+        return ns
+
+    n = args.gpus
+    out = [(f"dp{n}-760m", variant(mode="dp", model="760m"))]
+    if n == 1:
+        out.append(("1gpu-1.3b", variant(mode="dp", model="1.3b")))
+    else:
+        out.append((f"tp{n}+sp-345m", variant(mode="tp", model="345m")))
+        out.append((f"cp{n}-1.3b", variant(mode="cp", model="1.3b")))
+    if n in (4, 8):
+        out.append((layout(variant(mode="pp"))["name"] + "-345m", variant(mode="pp", model="345m")))
+    out.append((f"dp{n}-345m-published-knobs", variant(mode="dp", model="345m", knobs="published")))
+    return out
+
+
 def init_normal(model, std: float = 0.02) -> None:
     import torch
     with torch.no_grad():
@@ -138,8 +205,113 @@ def init_normal(model, std: float = 0.02) -> None:
                 p.zero_()
 
 
+def describe(spec: dict) -> str:
+    k = spec["knobs"]
+    style = ("RoPE, SwiGLU, no bias, fused QKV" if spec["knob_set"] == "published"
+             else "GELU, learned positions, bias, fused QKV")
+    return (f"GPT-{spec['model']} (L{k['num_layers']} H{k['hidden_size']} h{k['num_heads']} F{k['ffn_hidden_size']} "
+            f"V{k['vocab_size']}, {style}" + (", tied" if k["tie_word_embeddings"] else ", untied") + ")")
+
+
 def emit(payload: dict) -> None:
     print(json.dumps(payload), flush=True)
+
+
+# ------------------------------------------------------------------ measuring --
+def measure(args, spec: dict, steps: int, warmup: int) -> dict:
+    """Build one configuration, time it three ways, tear it down."""
+    import torch
+    import torch.distributed as dist
+
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    lay, knobs, batch, seq = spec["lay"], spec["knobs"], spec["batch"], spec["seq"]
+    runner = (ReferenceRunner if args.impl == "reference" else B200Runner)(args, spec)
+    torch.cuda.reset_peak_memory_stats(device)
+    runner.build()
+
+    gen = torch.Generator().manual_seed(1000 + runner.dp_rank)
+    pool = [torch.randint(0, knobs["vocab_size"], (batch, seq), generator=gen).pin_memory() for _ in range(4)]
+    ids_dev = [p.to(device) for p in pool]
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n: int, sample_clocks: bool = False):
+        sampler = ClockSampler(local_rank) if sample_clocks else None
+        if sampler is not None:
+            sampler.start()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        last = None
+        for i in range(n):
+            last = fn(i)
+        end.record()
+        barrier()
+        t = torch.tensor([start.elapsed_time(end)], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item(), last, (sampler.stop() if sampler is not None else None)
+
+    # Set-up, not warm-up: the trainer runs a few eager steps and then captures
+    # the step into a CUDA graph; do that before the W warm-up steps so that the
+    # timed region never contains the capture, whatever W is.
+    runner.prepare(ids_dev[0])
+    barrier()
+
+    # ---- device-timed region: inputs already resident ----
+    for i in range(warmup):
+        runner.step_device(ids_dev[i % 4])
+    launches0 = runner.launch_counter()
+    ms, loss, clocks = timed(lambda i: runner.step_device(ids_dev[i % 4]), steps, sample_clocks=True)
+    per_step_launches = runner.launches_per_step(runner.launch_counter() - launches0, steps)
+    final_loss = float(loss.item()) if loss is not None else None
+
+    # ---- end to end: pinned host inputs in, loss out, every step ----
+    for i in range(2):
+        runner.step_host(pool[i % 4])
+    ms_e2e, _, _ = timed(lambda i: runner.step_host(pool[i % 4]), steps)
+
+    # ---- the reference's benchmark step: no optimizer update ----
+    for i in range(max(warmup, 3)):
+        runner.step_no_optimizer(ids_dev[i % 4])
+    ms_nopt, _, _ = timed(lambda i: runner.step_no_optimizer(ids_dev[i % 4]), steps)
+    runner.check()
+
+    peak = torch.tensor([torch.cuda.max_memory_allocated(device) + runner.extra_device_bytes()],
+                        dtype=torch.float64, device=device)
+    dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    tokens_per_step = batch * seq * lay["dp"]
+    out = {
+        "tokens_per_step": tokens_per_step,
+        "value": tokens_per_step * steps / (ms / 1e3), "ms_per_step": ms / steps,
+        "e2e_value": tokens_per_step * steps / (ms_e2e / 1e3), "e2e_ms_per_step": ms_e2e / steps,
+        "nopt_value": tokens_per_step * steps / (ms_nopt / 1e3), "nopt_ms_per_step": ms_nopt / steps,
+        "peak_mem_mb": peak.item() / 2 ** 20, "clocks": clocks, "loss": final_loss,
+        "launches_per_step": per_step_launches, "graphed": runner.graphed, "note": runner.note,
+        "h2d": int(pool[0].numel() * pool[0].element_size()),
+    }
+    barrier()
+    runner.close()
+    del runner, pool, ids_dev
+    gc.collect()
+    torch.cuda.empty_cache()
+    barrier()
+    return out
+
+
+def mode_entry(spec: dict, m: dict, steps: int) -> dict:
+    return {
+        "config": {"model": describe(spec), "global_batch": spec["batch"] * spec["lay"]["dp"],
+                   "per_rank_batch": spec["batch"], "seq_len": spec["seq"], "parallelism": spec["lay"]["name"]},
+        "value": round(m["value"], 1), "unit": "tokens/s", "ms_per_step": round(m["ms_per_step"], 3), "steps": steps,
+        "e2e": {"value": round(m["e2e_value"], 1), "ms_per_step": round(m["e2e_ms_per_step"], 3)},
+        "step_without_optimizer": {"value": round(m["nopt_value"], 1), "unit": "tokens/s",
+                                   "ms_per_step": round(m["nopt_ms_per_step"], 3)},
+        "peak_mem_mb": round(m["peak_mem_mb"], 1), "loss": m["loss"],
+        **({"note": m["note"]} if m["note"] else {}),
+    }
 
 
 # ------------------------------------------------------------------------ main --
@@ -178,122 +350,82 @@ def main() -> int:
     os.environ.setdefault("RANK", "0")
     os.environ.setdefault("WORLD_SIZE", "1")
     os.environ.setdefault("LOCAL_RANK", "0")
-
-    lay = layout(args)
-    seq = args.seq or (1024 if args.mode == "pp" and args.gpus > 1 else 2048)
-    if args.mode == "cp" and args.gpus > 1 and args.seq is None:
-        seq = 2048 * args.gpus  # per-rank 2048 tokens, as the reference scales CP
-    batch = args.batch or (8 if args.mode == "pp" and args.gpus > 1 else (1 if args.model == "1.3b" else 2))
-    knobs = model_knobs(args.model, seq, args.mode if args.gpus > 1 else "dp")
-
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
-        runner = ReferenceRunner(args, lay, knobs, batch, seq)
-    else:
-        runner = B200Runner(args, lay, knobs, batch, seq)
-    runner.build()
+    # One process group for the whole run; every configuration builds its
+    # parallel context (and its sub-groups) on top of it and tears it down again.
+    import datetime
+    dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank),
+                            timeout=datetime.timedelta(seconds=600))
 
-    device = torch.device("cuda", local_rank)
-    dp_rank = runner.dp_rank
-    gen = torch.Generator().manual_seed(1000 + dp_rank)
-    pool = [torch.randint(0, knobs["vocab_size"], (batch, seq), generator=gen).pin_memory() for _ in range(4)]
-    ids_dev = [p.to(device) for p in pool]
+    spec = spec_of(args)
+    head = measure(args, spec, args.steps, args.warmup)
 
-    def barrier():
-        dist.barrier()
-        torch.cuda.synchronize()
+    modes: dict[str, dict] = {}
+    if not args.explicit_mode and not args.no_modes:
+        sub_steps = max(1, min(args.mode_steps, args.steps))
+        for name, ns in extra_specs(args):
+            sub = spec_of(ns)
+            try:
+                modes[name] = mode_entry(sub, measure(ns, sub, sub_steps, max(3, min(args.warmup, 5))), sub_steps)
+            except Exception as exc:  # one configuration must not cost the whole line
+                modes[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+                # the ranks may have diverged: no further collective configuration is safe
+                break
 
-    # Set-up, not warm-up: the trainer runs a few eager steps and then captures
-    # the step into a CUDA graph; do that before the W warm-up steps so that the
-    # timed region never contains the capture, whatever W is.
-    runner.prepare(ids_dev[0])
-    barrier()
-
-    # ---- device-timed region: inputs already resident ----
-    for i in range(args.warmup):
-        runner.step_device(ids_dev[i % 4])
-    barrier()
-    from nano_megatron_b200.ops import native as _native
-    launches0 = _native.launches
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for i in range(args.steps):
-        loss = runner.step_device(ids_dev[i % 4])
-    end.record()
-    barrier()
-    ms = start.elapsed_time(end)
-    clocks = sampler.stop()
-    per_step_launches = runner.launches_per_step(_native.launches - launches0, args.steps)
-    t = torch.tensor([ms], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item()
-    final_loss = float(loss.item()) if loss is not None else None
-
-    # ---- end to end: pinned host inputs in, loss out, every step ----
-    for i in range(2):
-        runner.step_host(pool[i % 4])
-    barrier()
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record()
-    for i in range(args.steps):
-        runner.step_host(pool[i % 4])
-    e2.record()
-    barrier()
-    t2 = torch.tensor([s2.elapsed_time(e2)], device=device)
-    dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    ms_e2e = t2.item()
-    runner.check()
-
-    tokens_per_step = batch * seq * lay["dp"]
-    value = tokens_per_step * args.steps / (ms / 1e3)
-    e2e_value = tokens_per_step * args.steps / (ms_e2e / 1e3)
-    published = PUBLISHED.get((args.model, args.mode, args.gpus))
+    lay, knobs = spec["lay"], spec["knobs"]
+    published = PUBLISHED.get((args.model, args.mode, args.gpus)) if args.knobs == "gpt2" else None
     if rank == 0:
         out = {
-            "metric": "training tokens/sec/box (device-timed, max over ranks), fwd+bwd+grad-sync+AdamW, bf16",
-            "value": round(value, 1), "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
+            "metric": METRIC,
+            "value": round(head["value"], 1), "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(head["ms_per_step"], 3), "higher_is_better": True,
             "scaling": "weak" if args.mode in ("dp", "cp") else "strong",
-            "vs_baseline": round(value / published, 3) if published else None,
+            "vs_baseline": round(head["value"] / published, 3) if published else None,
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init normal(0,0.02) weights",
             "impl": args.impl,
-            "config": {"model": f"GPT-{args.model} (L{knobs['num_layers']} H{knobs['hidden_size']} "
-                                f"h{knobs['num_heads']} F{knobs['ffn_hidden_size']} V{knobs['vocab_size']}, GELU, "
-                                "learned positions, bias, fused QKV" + (", tied" if knobs["tie_word_embeddings"] else ", untied") + ")",
-                       "global_batch": batch * lay["dp"], "per_rank_batch": batch, "seq_len": seq,
-                       "parallelism": lay["name"], "optimizer": "AdamW in the timed region",
-                       "attention": "flash", "cuda_graph": runner.graphed,
+            "config": {"model": describe(spec),
+                       "global_batch": spec["batch"] * lay["dp"], "per_rank_batch": spec["batch"],
+                       "seq_len": spec["seq"], "parallelism": lay["name"], "optimizer": "AdamW in the timed region",
+                       "attention": "flash",
                        "l2": "working set (weights + activations, > 2 GB) exceeds the 126 MB L2; no flush needed",
                        "vs_baseline_note": "published number is the reference on 4x RTX A6000 without optimizer step"
                        if published else "no published number for this configuration"},
-            "clocks": clocks,
-            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e / args.steps, 3),
-                    "h2d_bytes_per_step": int(pool[0].numel() * pool[0].element_size()), "d2h_bytes_per_step": 4},
-            "gpu_launches": int(per_step_launches * args.steps),
-            "loss": final_loss,
+            "clocks": head["clocks"],
+            "e2e": {"value": round(head["e2e_value"], 1), "unit": "tokens/s",
+                    "ms_per_step": round(head["e2e_ms_per_step"], 3),
+                    "h2d_bytes_per_step": head["h2d"], "d2h_bytes_per_step": 4},
+            "step_without_optimizer": {"value": round(head["nopt_value"], 1), "unit": "tokens/s",
+                                       "ms_per_step": round(head["nopt_ms_per_step"], 3),
+                                       "what": "zero-grad, forward, loss, backward, gradient sync (the reference's "
+                                               "own benchmark step)"},
+            "peak_mem_mb": round(head["peak_mem_mb"], 1),
+            "gpu_launches": int(head["launches_per_step"] * args.steps),
+            "cuda_graph": head["graphed"],
+            "loss": head["loss"],
         }
-        if runner.note:
-            out["note"] = runner.note
+        if modes:
+            out["modes"] = modes
+        if head["note"]:
+            out["note"] = head["note"]
         emit(out)
-    # The result is out.  Tear down in order, but never let teardown (NCCL
-    # communicator destruction, unmapping peer memory, interpreter finalisers)
-    # hold the job: a timer ends the process if close() stalls, and the process
-    # leaves without running finalisers once close() has returned.
-    barrier()
-    _arm_exit_timer(60.0)
-    runner.close()
+
+    # The result is out.  Tear down in order and leave through the normal
+    # interpreter exit (exit handlers run).  A timer stands by only in case
+    # communicator destruction stalls: then it ends the process.
     sys.stdout.flush()
     sys.stderr.flush()
-    os._exit(0)
+    fallback = _arm_exit_timer(90.0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    fallback.cancel()
+    return 0
 
 
-def _arm_exit_timer(seconds: float) -> None:
-    import threading
-
+def _arm_exit_timer(seconds: float) -> threading.Timer:
     def fire() -> None:
+        sys.stderr.write("bench.py: teardown did not finish in time; leaving\n")
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
@@ -301,13 +433,15 @@ def _arm_exit_timer(seconds: float) -> None:
     t = threading.Timer(seconds, fire)
     t.daemon = True
     t.start()
+    return t
 
 
 class B200Runner:
-    """This framework through its public API (``Trainer`` / ``forward_backward_1f1b``)."""
+    """This framework through its public API (``Trainer`` / ``PipelineTrainer``)."""
 
-    def __init__(self, args, lay, knobs, batch, seq) -> None:
-        self.args, self.lay, self.knobs, self.batch, self.seq = args, lay, knobs, batch, seq
+    def __init__(self, args, spec) -> None:
+        self.args, self.spec = args, spec
+        self.lay, self.knobs, self.batch, self.seq = spec["lay"], spec["knobs"], spec["batch"], spec["seq"]
         self.note = None
         self.graphed = False
 
@@ -324,50 +458,39 @@ class B200Runner:
             tensor_parallel_size=lay["tp"], context_parallel_size=lay["cp"], pipeline_parallel_size=lay["pp"],
             sequence_parallel=lay["sp"]), dist_backend="nccl")
         self.dp_rank = self.ctx.data_parallel_rank
+        self.workspaces = {}
         if not self.args.no_symm and self.ctx.world_size > 1:
             try:
                 from nano_megatron_b200.distributed.symm_mem import enable_symmetric_memory
-                enable_symmetric_memory(self.ctx)
+                self.workspaces = enable_symmetric_memory(self.ctx)
             except Exception as exc:  # plain NCCL stays available
                 self.note = f"symmetric memory unavailable ({type(exc).__name__}: {exc}); NCCL collectives used"
         seed_all(42)
         cfg = ReferenceGPTConfig(**self.knobs)
-        with torch.device("cpu"):
+        dev = torch.device("cuda", self.ctx.local_rank)
+        with torch.device(dev):
             ref = ReferenceGPT(cfg)
         init_normal(ref)
-        dev = torch.device("cuda", self.ctx.local_rank)
         if lay["pp"] > 1:
-            from nano_megatron_b200.distributed import DistributedDataParallel
-            from nano_megatron_b200.reference import AdamW
-            self.stage = build_pipeline_stage_from_reference(ref, self.ctx).to(dev, dtype=torch.bfloat16)
-            self.ddp = DistributedDataParallel(self.stage, self.ctx)
-            self.opt = AdamW(self.stage.named_parameters(), lr=1e-4, weight_decay=0.01)
-            self.trainer = None
+            from nano_megatron_b200.engine import PipelineTrainer
+            stage = build_pipeline_stage_from_reference(ref, self.ctx).to(dev, dtype=torch.bfloat16)
+            self.trainer = PipelineTrainer(stage, self.ctx, num_microbatches=self.spec["microbatches"], lr=1e-4,
+                                           weight_decay=0.01, use_cuda_graph=not self.args.no_graph)
         else:
             model = build_tp_gpt_from_reference(ref, self.ctx).to(dev, dtype=torch.bfloat16)
             self.trainer = Trainer(model, self.ctx, lr=1e-4, weight_decay=0.01,
                                    use_cuda_graph=not self.args.no_graph)
         del ref
-        self._ids_static = None
-
-    def _pp_step(self, ids):
-        from nano_megatron_b200.schedules import forward_backward_1f1b
-        self.ddp.zero_grad()
-        loss = forward_backward_1f1b(stage=self.stage, ctx=self.ctx, input_ids=ids, labels=ids,
-                                     num_microbatches=self.args.microbatches, ddp=self.ddp)
-        self.opt.step()
-        return loss
 
     def step_device(self, ids_dev):
-        if self.trainer is None:
-            return self._pp_step(ids_dev)
         loss = self.trainer.step(ids_dev)
         self.graphed = self.trainer.graphed
         return loss
 
+    def step_no_optimizer(self, ids_dev):
+        return self.trainer.forward_backward(ids_dev)
+
     def prepare(self, ids_dev) -> None:
-        if self.trainer is None:
-            return
         for _ in range(6):
             if self.trainer.graphed or self.trainer.graph_error or self.args.no_graph:
                 break
@@ -375,32 +498,38 @@ class B200Runner:
         self.graphed = self.trainer.graphed
 
     def step_host(self, ids_pinned):
-        import torch
-        if self.trainer is None:
-            loss = self._pp_step(ids_pinned.to(torch.device("cuda", self.ctx.local_rank), non_blocking=True))
-            return None if loss is None else loss.item()
-        return self.trainer.step(ids_pinned).item()
+        loss = self.trainer.step(ids_pinned)
+        return None if loss is None else loss.item()
+
+    def launch_counter(self) -> int:
+        from nano_megatron_b200.ops import native
+        return native.launches
 
     def launches_per_step(self, counted: int, steps: int) -> float:
-        if self.trainer is not None and self.trainer.graphed:
+        if self.trainer.graphed:
             return float(self.trainer.kernels_in_graph)
         return counted / max(steps, 1)
+
+    def extra_device_bytes(self) -> int:
+        return sum(ws.allocated_bytes() for ws in self.workspaces.values())
 
     def check(self) -> None:
         from nano_megatron_b200.ops import native
         native.check_status()
-        if self.trainer is not None and self.trainer.graph_error and self.note is None:
-            self.note = f"CUDA graph capture failed, eager launches used: {self.trainer.graph_error}"
+        if self.trainer.graph_error and self.note is None:
+            self.note = f"not every step kind runs from a CUDA graph: {self.trainer.graph_error}"
 
     def close(self) -> None:
+        self.trainer = None
         self.P.destroy_parallel()
 
 
 class ReferenceRunner:
     """The unmodified reference package: its models, DDP, schedule and AdamW."""
 
-    def __init__(self, args, lay, knobs, batch, seq) -> None:
-        self.args, self.lay, self.knobs, self.batch, self.seq = args, lay, knobs, batch, seq
+    def __init__(self, args, spec) -> None:
+        self.args, self.spec = args, spec
+        self.lay, self.knobs, self.batch, self.seq = spec["lay"], spec["knobs"], spec["batch"], spec["seq"]
         self.note = None
         self.graphed = False
 
@@ -419,10 +548,12 @@ class ReferenceRunner:
             sequence_parallel=lay["sp"]), dist_backend="nccl")
         self.dp_rank = self.ctx.data_parallel_rank
         torch.manual_seed(42)
+        torch.cuda.manual_seed_all(42)
         cfg = ReferenceGPTConfig(**self.knobs)
-        ref = ReferenceGPT(cfg)
-        init_normal(ref)
         dev = torch.device("cuda", self.ctx.local_rank)
+        with torch.device(dev):
+            ref = ReferenceGPT(cfg)
+        init_normal(ref)
         self.dev = dev
         if lay["pp"] > 1:
             self.stage = build_pipeline_stage_from_reference(ref, self.ctx).to(dev, dtype=torch.bfloat16)
@@ -435,19 +566,22 @@ class ReferenceRunner:
         self.opt = AdamW(self.module.named_parameters(), lr=1e-4, weight_decay=0.01)
         self._plain_ce = shifted_cross_entropy
 
-    def _step(self, ids):
+    def _forward_backward(self, ids):
         if self.lay["pp"] > 1:
             from nano_megatron.schedules import forward_backward_1f1b
-            loss = forward_backward_1f1b(stage=self.stage, ctx=self.ctx, input_ids=ids, labels=ids,
-                                         num_microbatches=self.args.microbatches, ddp=self.ddp)
+            return forward_backward_1f1b(stage=self.stage, ctx=self.ctx, input_ids=ids, labels=ids,
+                                         num_microbatches=self.spec["microbatches"], ddp=self.ddp)
+        logits = self.ddp(ids)
+        if hasattr(self.module, "shifted_cross_entropy"):
+            loss = self.module.shifted_cross_entropy(logits, ids)
         else:
-            logits = self.ddp(ids)
-            if hasattr(self.module, "shifted_cross_entropy"):
-                loss = self.module.shifted_cross_entropy(logits, ids)
-            else:
-                loss = self._plain_ce(logits, ids)
-            loss.backward()
-            self.ddp.finish_grad_sync()
+            loss = self._plain_ce(logits, ids)
+        loss.backward()
+        self.ddp.finish_grad_sync()
+        return loss
+
+    def _step(self, ids):
+        loss = self._forward_backward(ids)
         self.opt.step()
         self.ddp.zero_grad(set_to_none=True)
         return loss
@@ -455,12 +589,24 @@ class ReferenceRunner:
     def step_device(self, ids_dev):
         return self._step(ids_dev)
 
+    def step_no_optimizer(self, ids_dev):
+        # the loop of the reference's own benchmark scripts (scripts/benchmark_dp.py:212-223)
+        loss = self._forward_backward(ids_dev)
+        self.ddp.zero_grad(set_to_none=True)
+        return loss
+
     def step_host(self, ids_pinned):
         loss = self._step(ids_pinned.to(self.dev, non_blocking=True))
         return None if loss is None else loss.item()
 
+    def launch_counter(self) -> int:
+        return 0
+
     def launches_per_step(self, counted: int, steps: int) -> float:
         return 0.0
+
+    def extra_device_bytes(self) -> int:
+        return 0
 
     def check(self) -> None:
         pass
@@ -469,6 +615,7 @@ class ReferenceRunner:
         pass
 
     def close(self) -> None:
+        self.opt = self.ddp = self.module = self.stage = None
         self._destroy()
 
 

@@ -84,7 +84,8 @@ extern "C" int nmb_col_sum_noalloc_max_cols(void) { return NMB_NOALLOC_MAX_COLS;
 extern "C" const char* nmb_col_sum_noalloc_strerror(int code) {
   switch (code) {
     case NMB_NOALLOC_OK: return "ok";
-    case NMB_NOALLOC_BAD_SHAPE: return "cols and ld must be even and the pointers non-null";
+    case NMB_NOALLOC_BAD_SHAPE:
+      return "cols and ld must be even, ld >= cols, dy 4-byte aligned, out 2-byte aligned, pointers non-null";
     case NMB_NOALLOC_TOO_LARGE: return "cols exceeds NMB_NOALLOC_MAX_COLS (8192): the built-in scratch is too small";
     case NMB_NOALLOC_NO_SCRATCH: return "the built-in scratch array could not be resolved on the current device";
     default: return "CUDA launch error (code - 400 is the cudaError_t)";
@@ -93,8 +94,14 @@ extern "C" const char* nmb_col_sum_noalloc_strerror(int code) {
 
 extern "C" int nmb_col_sum_noalloc(const void* dy, int ld, void* out, int rows, int cols, int accumulate,
                                    void* stream) {
-  if (rows <= 0 || cols <= 0) return NMB_NOALLOC_OK;
-  if (dy == nullptr || out == nullptr || (cols % 2) != 0 || (ld % 2) != 0 || ld < cols) return NMB_NOALLOC_BAD_SHAPE;
+  if (cols <= 0) return NMB_NOALLOC_OK;
+  if (out == nullptr || (reinterpret_cast<uintptr_t>(out) & 1) != 0) return NMB_NOALLOC_BAD_SHAPE;
+  if (rows < 0) rows = 0;
+  // Stage 1 reads dy two bf16 at a time (4-byte loads at dy + r * ld + c with c
+  // even): the base must be 4-byte aligned and the pitch even, or the load is a
+  // misaligned address on the device.
+  if (rows > 0 && (dy == nullptr || (reinterpret_cast<uintptr_t>(dy) & 3) != 0)) return NMB_NOALLOC_BAD_SHAPE;
+  if ((cols % 2) != 0 || (ld % 2) != 0 || ld < cols) return NMB_NOALLOC_BAD_SHAPE;
   if (cols > NMB_NOALLOC_MAX_COLS) return NMB_NOALLOC_TOO_LARGE;
   float* scratch = scratch_for_current_device();
   if (scratch == nullptr) return NMB_NOALLOC_NO_SCRATCH;

@@ -224,24 +224,25 @@ peer_allgather_kernel(const uint4* __restrict__ src, PeerPtrs dst, PeerPtrs pads
   if (threadIdx.x == 0) *my_epoch = e0 + 1;
 }
 
-// Vocabulary-parallel embedding under sequence parallelism without a
-// reduction: every token's row has exactly one producer (the rank that owns
-// its vocabulary id), which writes token + position embedding straight into
-// the sequence-shard owner's output buffer.
+// Vocabulary-parallel embedding without a reduction: every token's row has
+// exactly one producer (the rank that owns its vocabulary id), which writes
+// token + position embedding straight into the output buffers of the ranks that
+// need the row -- the owner of the token's sequence shard (sequence parallel,
+// `to_all == 0`, output `[B * S/ranks, H]`) or every rank (`to_all != 0`,
+// output `[B * S, H]`).
 __global__ void embedding_scatter_kernel(const long long* __restrict__ ids, const long long* __restrict__ positions,
                                          const __nv_bfloat16* __restrict__ tok, const __nv_bfloat16* __restrict__ pos,
-                                         PeerPtrs out, int n_tokens, int H, int vocab_start, int vloc, int seq_len,
-                                         int shard_len) {
+                                         PeerPtrs out, int n_ranks, int n_tokens, int H, int vocab_start, int vloc,
+                                         int seq_len, int shard_len, int to_all) {
   const int row = blockIdx.x;
   if (row >= n_tokens) return;
   const long long id = ids[row] - vocab_start;
   if (id < 0 || id >= vloc) return;
   const int s = row % seq_len;
   const int owner = s / shard_len;
-  const long long local = static_cast<long long>(row / seq_len) * shard_len + s % shard_len;
+  const long long local = to_all ? row : static_cast<long long>(row / seq_len) * shard_len + s % shard_len;
   const uint4* tr = reinterpret_cast<const uint4*>(tok + id * H);
   const uint4* pr = pos != nullptr ? reinterpret_cast<const uint4*>(pos + positions[row] * H) : nullptr;
-  uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out.p[owner]) + local * H);
   for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
     uint4 v = tr[i];
     if (pr != nullptr) {
@@ -257,7 +258,12 @@ __global__ void embedding_scatter_kernel(const long long* __restrict__ ids, cons
       }
       v = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    dst[i] = v;
+    if (to_all) {
+      for (int r = 0; r < n_ranks; ++r)
+        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out.p[r]) + local * H)[i] = v;
+    } else {
+      reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out.p[owner]) + local * H)[i] = v;
+    }
   }
 }
 
@@ -420,14 +426,14 @@ extern "C" int nmb_peer_allgather(const void* src, void* const* dsts, void* cons
 
 extern "C" int nmb_embedding_scatter(const long long* ids, const long long* positions, const void* tok,
                                      const void* pos, void* const* outs, int n_ranks, int n_tokens, int H,
-                                     int vocab_start, int vloc, int seq_len, int shard_len, void* stream) {
+                                     int vocab_start, int vloc, int seq_len, int shard_len, int to_all, void* stream) {
   if (n_tokens <= 0) return 0;
-  if (H % 8 != 0 || n_ranks < 1 || n_ranks > kMaxRanks) return kBadArgument;
+  if (H % 8 != 0 || n_ranks < 1 || n_ranks > kMaxRanks || shard_len < 1) return kBadArgument;
   PeerPtrs o;
   fill(o, outs, n_ranks);
   embedding_scatter_kernel<<<n_tokens, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      ids, positions, static_cast<const __nv_bfloat16*>(tok), static_cast<const __nv_bfloat16*>(pos), o, n_tokens, H,
-      vocab_start, vloc, seq_len, shard_len);
+      ids, positions, static_cast<const __nv_bfloat16*>(tok), static_cast<const __nv_bfloat16*>(pos), o, n_ranks,
+      n_tokens, H, vocab_start, vloc, seq_len, shard_len, to_all);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + e;
 }

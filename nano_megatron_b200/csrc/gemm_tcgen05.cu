@@ -14,7 +14,7 @@
 // residual elementwise kernels that follow them
 // (nano_megatron/reference/layers.py:39, :343, :352).
 //
-// Structure: persistent CTAs (one per SM), 192 threads:
+// Structure: persistent CTAs (one per SM), 320 threads:
 //   warp 0      TMA producer (one elected lane), STAGES-deep smem ring
 //   warp 1      TMEM owner + single-thread tcgen05.mma issuer
 //   warps 2..9  epilogue: tcgen05.ld -> registers -> bias/GELU/residual -> global
@@ -62,11 +62,38 @@ struct GemmEpilogue {
 //    CTAs walk the tiles local-shard-first and wait for a tile's flag before
 //    issuing its first TMA load, so the transfer hides behind the math.  Every
 //    remote tile crosses NVLink once and is then read from local memory.
-//  * reduce-scatter / all-reduce of C: the epilogue stores each partial tile
-//    straight into the owner rank's staging slot [my_rank] (peer stores); when
-//    every rank has stored all its tiles (one flag round), each rank sums the
-//    slots of its rows, adds bias / residual and writes the result -- to its own
-//    shard (reduce-scatter) or to every rank's output (all-reduce).
+//  * reduce-scatter / all-reduce of C: every 128-row block of C has an owner
+//    rank (the owner of its sequence shard).  A rank computes the blocks of the
+//    other owners FIRST and stores each partial tile straight into slot
+//    [my_rank] of the owner's staging buffer (peer stores), followed by one
+//    release store to the tile's flag on the owner.  Its own blocks come LAST:
+//    by then the peers' partials have normally landed, the epilogue of an own
+//    tile waits for the tile's flags (bounded), adds the peers' partials, bias
+//    and residual to its accumulator and writes the final tile -- to its own
+//    shard (reduce-scatter) or to every rank's output followed by a second flag
+//    (all-reduce; the kernel ends by waiting for the final tiles of the other
+//    owners).  There is no grid-wide round and no separate reduction pass.
+//
+// Flags hold the launch's epoch (a device-side counter that the last CTA to
+// leave the kernel advances, so a replayed CUDA graph keeps counting); they
+// only grow and never need clearing.  Ranks of a group must launch the same
+// fused GEMMs in the same order.
+//
+// Buffer reuse.  Peers write into this rank's staging / output buffers, so a
+// peer may only start writing for launch j once this rank is done with the
+// previous launch that used the same buffers (including whatever its stream
+// did with the result afterwards).  Every launch therefore announces "I have
+// started the launch with epoch e" to all peers (`rs_started`), every buffer
+// remembers the epoch of the last launch that used it (`rs_last`, the same
+// value on all ranks because the sequences are identical), and before its first
+// peer store a CTA waits until every peer has started a launch later than that
+// one.  The caller alternates two buffers per shape, which makes this wait a
+// formality (finishing a launch needs the peers' tiles of that launch, so a
+// rank is never more than one launch ahead); with a single buffer, or when a
+// replayed CUDA graph follows another one that ended on the same buffer, it
+// degrades to a rendezvous at the start of the launch instead of a race.
+constexpr int kMaxFusedTiles = 4096;  // per owner: (rows_per_rank / 128) * ceil(N / BN)
+
 struct FusedComm {
   const void* ag_src[kMaxRanks];
   void* ag_dst;
@@ -75,16 +102,22 @@ struct FusedComm {
   int rs_mode;  // 0 off, 1 reduce-scatter, 2 all-reduce
   void* rs_stage[kMaxRanks];
   void* rs_out[kMaxRanks];
+  uint32_t* rs_flags[kMaxRanks];  // per rank: [2][kMaxFusedTiles][kMaxRanks]: partial stored / final stored
+  uint32_t* rs_started[kMaxRanks];  // per rank: [kMaxRanks] "rank r has started the launch with this epoch"
+  uint32_t* rs_last[2];             // local: epoch of the last launch that used the staging / output buffer
   const __nv_bfloat16* rs_bias;
   const __nv_bfloat16* rs_residual;
   void* pads[kMaxRanks];
-  uint32_t* epochs;    // [kChannels][kMaxBlocks] device-side epoch counters
-  uint32_t* counters;  // two zero-initialised words for the intra-GPU arrival counts
+  uint32_t* sync;  // [0] epoch of the last finished fused launch, [1] CTAs of this launch that have left
   int channel;
   int rank, n_ranks;
   int seq_len, shard_len, rows_per_rank;
   long long budget;
 };
+
+__device__ __forceinline__ uint32_t* fused_flag(const FusedComm& fc, int on_rank, int kind, int tile, int from_rank) {
+  return fc.rs_flags[on_rank] + (static_cast<size_t>(kind) * kMaxFusedTiles + tile) * kMaxRanks + from_rank;
+}
 
 // Rows are [batch][sequence]; a sequence is cut into n_ranks contiguous shards.
 __device__ __forceinline__ int row_owner(const FusedComm& fc, int row) { return (row % fc.seq_len) / fc.shard_len; }
@@ -101,19 +134,46 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarOffset = STAGES * kStageBytes;
-  // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot, abort
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
+  // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tile_done[2], tmem slot, abort, epoch
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 6) * 8 + 32;
 };
 
 // Copy CTA of the fused all-gather: pulls remote 128-row tiles of A into the
-// local full buffer and publishes one ready flag per tile.
-__device__ void gather_copy_role(const FusedComm& fc, int M, int K, int copy_idx, int* status) {
+// local full buffer and publishes one ready flag per tile.  NVLink needs a
+// couple of megabytes in flight to run at full rate (bandwidth x ~2.5 us of
+// latency), far more than a few CTAs' worth of register loads: one thread per
+// copy CTA drives bulk asynchronous copies instead (peer memory -> shared
+// memory -> local memory, a ring of 32 KB pieces, five loads in flight per CTA;
+// plain bulk copies, no cluster multicast).
+constexpr int kCopyPiece = 32768;
+constexpr int kCopyStages = 6;
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ uint32_t gather_copy_role(const FusedComm& fc, int M, int K, int copy_idx, int* status, uint8_t* smem) {
   __shared__ uint32_t epoch_s;
   __shared__ int ok_s;
-  uint32_t* chan_epoch = fc.epochs + fc.channel * kMaxBlocks;
+  __shared__ int abort_s;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kCopyStages * kCopyPiece);
   if (threadIdx.x == 0) {
-    epoch_s = chan_epoch[0] + 1;
+    epoch_s = fc.sync[0] + 1;
     ok_s = 1;
+    abort_s = 0;
+    for (int i = 0; i < kCopyStages; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
   }
   __syncthreads();
   const uint32_t e = epoch_s;
@@ -128,135 +188,98 @@ __device__ void gather_copy_role(const FusedComm& fc, int M, int K, int copy_idx
     }
   }
   __syncthreads();
-  const int tiles_m = M / kBM;
   const int tpc = fc.shard_len / kBM;
   const int nb = M / fc.seq_len;
   const int per_owner = nb * tpc;
   const int remote = (fc.n_ranks - 1) * per_owner;
-  const size_t row_bytes = static_cast<size_t>(K) * 2;
-  const int vec_per_tile = static_cast<int>(kBM * row_bytes / 16);
-  for (int i = copy_idx; i < remote; i += fc.ag_copy_ctas) {
-    const int k = 1 + i / per_owner;  // distance from my rank
-    const int rem = i % per_owner;
-    const int owner = (fc.rank + k) % fc.n_ranks;
-    const int m_blk = ((rem / tpc) * fc.seq_len + owner * fc.shard_len) / kBM + rem % tpc;
-    if (ok_s) {
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(fc.ag_src[owner]) +
-                                                        static_cast<size_t>(m_blk) * kBM * row_bytes);
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(fc.ag_dst) + static_cast<size_t>(m_blk) * kBM * row_bytes);
-      constexpr int U = 4;
-      for (int base = threadIdx.x; base < vec_per_tile; base += blockDim.x * U) {
-        uint4 v[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (base + u * static_cast<int>(blockDim.x) < vec_per_tile) v[u] = src[base + u * blockDim.x];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          if (base + u * static_cast<int>(blockDim.x) < vec_per_tile) dst[base + u * blockDim.x] = v[u];
+  const size_t tile_bytes = static_cast<size_t>(kBM) * K * 2;
+  const int pieces = static_cast<int>((tile_bytes + kCopyPiece - 1) / kCopyPiece);
+  const int my_tiles = remote > copy_idx ? (remote - copy_idx + fc.ag_copy_ctas - 1) / fc.ag_copy_ctas : 0;
+  const int total = my_tiles * pieces;
+  if (threadIdx.x == 0) {
+    // item j = (j / pieces)-th tile of this CTA, piece j % pieces
+    auto locate = [&](int j, int& m_blk, size_t& off, uint32_t& bytes, int& owner) {
+      const int i = copy_idx + (j / pieces) * fc.ag_copy_ctas;
+      const int k = 1 + i / per_owner;  // distance from my rank
+      const int rem = i % per_owner;
+      owner = (fc.rank + k) % fc.n_ranks;
+      m_blk = ((rem / tpc) * fc.seq_len + owner * fc.shard_len) / kBM + rem % tpc;
+      const size_t in_tile = static_cast<size_t>(j % pieces) * kCopyPiece;
+      off = static_cast<size_t>(m_blk) * tile_bytes + in_tile;
+      const size_t left = tile_bytes - in_tile;
+      bytes = static_cast<uint32_t>(left < kCopyPiece ? left : kCopyPiece);
+    };
+    int loaded = 0;
+    bool ok = ok_s != 0;
+    for (int stored = 0; stored < total; ++stored) {
+      while (ok && loaded < total && loaded - stored < kCopyStages - 1) {
+        // the piece stored from this stage two stores ago has left shared memory
+        if (loaded >= kCopyStages) bulk_wait_read_1();
+        int m_blk, owner;
+        size_t off;
+        uint32_t bytes;
+        locate(loaded, m_blk, off, bytes, owner);
+        uint64_t* bar = &bars[loaded % kCopyStages];
+        mbar_expect_tx(bar, bytes);
+        bulk_load(smem + (loaded % kCopyStages) * kCopyPiece, static_cast<const uint8_t*>(fc.ag_src[owner]) + off, bytes,
+                  bar);
+        ++loaded;
+      }
+      int m_blk, owner;
+      size_t off;
+      uint32_t bytes;
+      locate(stored, m_blk, off, bytes, owner);
+      if (ok) {
+        if (!mbar_wait(&bars[stored % kCopyStages], (stored / kCopyStages) & 1, &abort_s, status, 17)) ok = false;
+      }
+      if (ok) {
+        bulk_store(static_cast<uint8_t*>(fc.ag_dst) + off, smem + (stored % kCopyStages) * kCopyPiece, bytes);
+        bulk_commit();
+      }
+      if (stored % pieces == pieces - 1) {
+        // the tile is complete in local memory: publish it (also after a failed
+        // wait, so that no GEMM CTA spins on it; the status word tells the host)
+        bulk_wait_all();
+        __threadfence();
+        fence_proxy_async_all();
+        st_release_gpu(&fc.ag_ready[m_blk], e);
       }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence();
-      fence_proxy_async_all();
-      // even after a failed wait the flag is published so that no GEMM CTA spins
-      st_release_gpu(&fc.ag_ready[m_blk], e);
+    bulk_wait_all();
+    if (!ok) {
+      // loads may still be landing in shared memory: let them before the CTA exits
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
     }
   }
-  (void)tiles_m;
   // Closing round: no peer is still reading this rank's shard when a later
-  // kernel overwrites it.  (The channel epoch itself is advanced by a separate
-  // one-thread kernel after this launch, once every CTA has read it.)
+  // kernel overwrites it.  The copy CTAs are done long before the compute CTAs,
+  // so this wait is normally hidden.
   __syncthreads();
-  if (threadIdx.x < fc.n_ranks) {
+  if (threadIdx.x < fc.n_ranks && ok_s) {
     __threadfence_system();
-    st_release_sys(pad_slot(fc.pads[threadIdx.x], fc.channel, 1 + copy_idx, fc.rank), e + 1);
-    if (!wait_flag_sys(pad_slot(fc.pads[fc.rank], fc.channel, 1 + copy_idx, threadIdx.x), e + 1, fc.budget))
+    st_release_sys(pad_slot(fc.pads[threadIdx.x], fc.channel, 65 + copy_idx, fc.rank), e);
+    if (!wait_flag_sys(pad_slot(fc.pads[fc.rank], fc.channel, 65 + copy_idx, threadIdx.x), e, fc.budget))
       report_status(status, kPeerTimeout, 7);
   }
+  return e;
 }
 
-// Second half of GEMM -> reduce-scatter / all-reduce, run by every GEMM CTA
-// after its last tile.
-__device__ void reduce_phase(const FusedComm& fc, int n_ctas, int N, int* status) {
-  __shared__ uint32_t epoch_s;
-  __shared__ int ok_s;
-  uint32_t* chan_epoch = fc.epochs + fc.channel * kMaxBlocks;
-  if (threadIdx.x == 0) {
-    epoch_s = chan_epoch[0];
-    ok_s = 1;
-  }
-  __syncthreads();  // also: this CTA's tile stores precede the fence below
-  const uint32_t e = epoch_s + 1;
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const unsigned arrived = atomicAdd(&fc.counters[0], 1u);
-    if (arrived == static_cast<unsigned>(n_ctas) - 1) {
-      // last CTA of this GPU: every tile of this rank has been stored
-      fc.counters[0] = 0;
-      __threadfence_system();
-      for (int p = 0; p < fc.n_ranks; ++p) st_release_sys(pad_slot(fc.pads[p], fc.channel, 0, fc.rank), e);
-    }
-  }
-  if (threadIdx.x < fc.n_ranks) {
-    if (!wait_flag_sys(pad_slot(fc.pads[fc.rank], fc.channel, 0, threadIdx.x), e, fc.budget)) {
-      report_status(status, kPeerTimeout, 8);
-      ok_s = 0;
-    }
-  }
+// Every CTA of a fused launch (compute and copy CTAs alike, also after an
+// aborted wait) leaves through here: the last one advances the epoch.
+__device__ __forceinline__ void fused_leave(const FusedComm& fc, uint32_t epoch) {
   __syncthreads();
-  if (ok_s) {
-    const long long slot_vecs = static_cast<long long>(fc.rows_per_rank) * N / 8;
-    const int row_vecs = N / 8;
-    const uint4* stage = static_cast<const uint4*>(fc.rs_stage[fc.rank]);
-    for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < slot_vecs;
-         v += static_cast<long long>(n_ctas) * blockDim.x) {
-      float acc[8];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-      auto add = [&](const uint4& u) {
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float2 f = unpack_bf16x2(w[k]);
-          acc[2 * k] += f.x;
-          acc[2 * k + 1] += f.y;
-        }
-      };
-      for (int s2 = 0; s2 < fc.n_ranks; ++s2) add(stage[s2 * slot_vecs + v]);
-      const int local = static_cast<int>(v / row_vecs);
-      const int cv = static_cast<int>(v % row_vecs);
-      if (fc.rs_bias != nullptr) add(reinterpret_cast<const uint4*>(fc.rs_bias)[cv]);
-      uint4 o;
-      if (fc.rs_mode == 1) {
-        if (fc.rs_residual != nullptr) add(reinterpret_cast<const uint4*>(fc.rs_residual)[v]);
-        o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                       pack_bf16x2(acc[6], acc[7]));
-        static_cast<uint4*>(fc.rs_out[fc.rank])[v] = o;
-      } else {
-        const long long gv = static_cast<long long>(row_global(fc, fc.rank, local)) * row_vecs + cv;
-        if (fc.rs_residual != nullptr) add(reinterpret_cast<const uint4*>(fc.rs_residual)[gv]);
-        o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                       pack_bf16x2(acc[6], acc[7]));
-        for (int p = 0; p < fc.n_ranks; ++p) static_cast<uint4*>(fc.rs_out[(fc.rank + p) % fc.n_ranks])[gv] = o;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned left = atomicAdd(&fc.sync[1], 1u);
+    if (left == gridDim.x - 1) {
+      fc.sync[1] = 0;
+      fc.sync[0] = epoch;
+      if (fc.rs_mode != 0) {
+        *fc.rs_last[0] = epoch;
+        if (fc.rs_last[1] != nullptr) *fc.rs_last[1] = epoch;
       }
+      __threadfence();
     }
-  }
-  // Closing round: (all-reduce) every rank's rows have landed everywhere.  The
-  // channel epoch is advanced by a one-thread kernel after this launch.
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    const unsigned arrived = atomicAdd(&fc.counters[1], 1u);
-    if (arrived == static_cast<unsigned>(n_ctas) - 1) {
-      fc.counters[1] = 0;
-      __threadfence_system();
-      for (int p = 0; p < fc.n_ranks; ++p) st_release_sys(pad_slot(fc.pads[p], fc.channel, 0, fc.rank), e + 1);
-    }
-  }
-  if (fc.rs_mode == 2 && threadIdx.x < fc.n_ranks) {
-    if (!wait_flag_sys(pad_slot(fc.pads[fc.rank], fc.channel, 0, threadIdx.x), e + 1, fc.budget))
-      report_status(status, kPeerTimeout, 9);
   }
 }
 
@@ -357,12 +380,6 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
         }
       } else {
         __nv_bfloat16* c_row = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc;
-        if (fc.rs_mode != 0) {
-          // partial tile -> slot [my rank] of the owner's staging buffer
-          const int owner = row_owner(fc, row);
-          c_row = static_cast<__nv_bfloat16*>(fc.rs_stage[owner]) +
-                  (static_cast<size_t>(fc.rank) * fc.rows_per_rank + row_local(fc, row)) * N;
-        }
         uint4* cp = reinterpret_cast<uint4*>(c_row + col0);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -414,26 +431,133 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
   }
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+// Epilogue of a tile whose rows take part in a fused reduce-scatter /
+// all-reduce (N is a multiple of 32 there, rows are whole 128-row blocks).
+//   own == false: the tile belongs to another rank: store the bf16 partial into
+//                 slot [my rank] of the owner's staging buffer;
+//   own == true : add the peers' partials (already in my staging buffer), bias
+//                 and residual, and write the final tile to my shard
+//                 (reduce-scatter) or to every rank's output (all-reduce).
+// In the accumulator a lane owns a ROW (32 consecutive columns per tcgen05.ld),
+// so storing from registers would issue 16-byte writes to 32 different rows per
+// instruction -- over NVLink that is one tiny packet per lane.  The warp
+// therefore transposes 64 columns at a time through a 4 KB shared-memory buffer
+// of its own (16-byte chunks XOR-swizzled by the row) and writes rows out in
+// 128-byte runs, four rows per instruction.
+constexpr int kEpiStageBytes = 8 * 4096;  // one 32 x 64 bf16 buffer per epilogue warp
+
+template <int BN>
+__device__ __forceinline__ void epilogue_columns_reduce(const GemmEpilogue& ep, const FusedComm& fc, uint32_t t_row,
+                                                        int m0, int quad, int lane, int owner, int n0, int half, int N,
+                                                        bool own, uint4* wbuf) {
+  const int row = m0 + quad * 32 + lane;         // the accumulator row this lane drains
+  const int lrow = row_local(fc, row);
+  const int lrow0 = lrow - lane;                  // local index of the warp's first row (a tile never straddles shards)
+  const int grow0 = row - lane;
+#pragma unroll 1
+  for (int c2 = half * (BN / 128); c2 < (half + 1) * (BN / 128); ++c2) {
+    const int col0 = n0 + c2 * 64;
+    if (col0 >= N) break;  // uniform across the warp
+    const int ncols = (N - col0) < 64 ? (N - col0) : 64;  // 32 or 64
+#pragma unroll 1
+    for (int h2 = 0; h2 * 32 < ncols; ++h2) {
+      const int cc = col0 + h2 * 32;
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + (c2 * 2 + h2) * 32, r);
+      tmem_ld_wait();
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
+      if (own) {
+        auto add4 = [&](const uint4* src) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 u = src[q];
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float2 f = unpack_bf16x2(w[t]);
+              v[q * 8 + t * 2] += f.x;
+              v[q * 8 + t * 2 + 1] += f.y;
+            }
+          }
+        };
+        const __nv_bfloat16* mine = static_cast<const __nv_bfloat16*>(fc.rs_stage[fc.rank]);
+        for (int p = 1; p < fc.n_ranks; ++p) {
+          const int src = (fc.rank + p) % fc.n_ranks;
+          add4(reinterpret_cast<const uint4*>(mine + (static_cast<size_t>(src) * fc.rows_per_rank + lrow) * N + cc));
+        }
+        if (fc.rs_bias != nullptr) add4(reinterpret_cast<const uint4*>(fc.rs_bias + cc));
+        // reduce-scatter: residual is this rank's [rows_per_rank, N] shard; all-reduce: the full [M, N]
+        const size_t rrow = fc.rs_mode == 1 ? static_cast<size_t>(lrow) : static_cast<size_t>(row);
+        if (fc.rs_residual != nullptr) add4(reinterpret_cast<const uint4*>(fc.rs_residual + rrow * N + cc));
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 o;
+        o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+        o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+        o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+        o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+        wbuf[lane * 8 + ((h2 * 4 + q) ^ (lane & 7))] = o;
+      }
+    }
+    __syncwarp();
+    const int segs = ncols / 8;  // 16-byte chunks per row: 4 or 8
+    const int seg = lane & 7;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + (lane >> 3);
+      if (seg >= segs) continue;
+      const uint4 o = wbuf[rr * 8 + (seg ^ (rr & 7))];
+      const size_t col = static_cast<size_t>(col0) + seg * 8;
+      if (!own) {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(fc.rs_stage[owner]) +
+                             (static_cast<size_t>(fc.rank) * fc.rows_per_rank + lrow0 + rr) * N + col;
+        *reinterpret_cast<uint4*>(dst) = o;
+      } else if (fc.rs_mode == 1) {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(fc.rs_out[fc.rank]) + static_cast<size_t>(lrow0 + rr) * N + col;
+        *reinterpret_cast<uint4*>(dst) = o;
+      } else {
+        for (int p = 0; p < fc.n_ranks; ++p) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(fc.rs_out[(fc.rank + p) % fc.n_ranks]) +
+                               static_cast<size_t>(grow0 + rr) * N + col;
+          *reinterpret_cast<uint4*>(dst) = o;
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// FUSED selects the instantiation that carries the collective code paths (copy
+// CTAs, reduce epilogue); the plain one stays at the register count that lets a
+// block of the overlapped gradient all-reduce share its SM.
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  GemmEpilogue ep, const __grid_constant__ FusedComm fc, int M, int N, int K, int* status) {
   using L = GemmSmem<BN, STAGES>;
-  const int n_gemm_ctas = gridDim.x - fc.ag_copy_ctas;
-  if (static_cast<int>(blockIdx.x) >= n_gemm_ctas) {
-    gather_copy_role(fc, M, K, blockIdx.x - n_gemm_ctas, status);
-    return;
-  }
+  const int n_gemm_ctas = FUSED ? gridDim.x - fc.ag_copy_ctas : gridDim.x;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // SWIZZLE_128B operands need 1024-byte aligned stage bases.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  if (FUSED && static_cast<int>(blockIdx.x) >= n_gemm_ctas) {
+    static_assert(kCopyStages * kCopyPiece + kCopyStages * 8 <= L::kTotal, "copy ring must fit the GEMM's shared memory");
+    const uint32_t e = gather_copy_role(fc, M, K, blockIdx.x - n_gemm_ctas, status, smem);
+    fused_leave(fc, e);
+    return;
+  }
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* tile_done = acc_empty + 2;  // fused reduce: the 8 epilogue warps have stored a tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_done + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* epoch_slot = tmem_slot + 2;
+  uint32_t* need_slot = tmem_slot + 3;  // fused reduce: peers must have started a launch with at least this epoch
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -442,12 +566,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + kBK - 1) / kBK;
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: powers of two
-  const bool gathered = fc.ag_copy_ctas > 0;
+  const bool gathered = FUSED && fc.ag_copy_ctas > 0;
+  const bool reducing = FUSED && fc.rs_mode != 0;
+  const bool fused = gathered || reducing;
   // tile -> (m block, n block).  Plain GEMM: m fastest.  Gathered A: all n
   // blocks of an m block together, m blocks ordered local shard first, then the
   // peers by distance, so the first waves need no remote data.
+  // Fused reduce: the other owners' blocks first (their partials have to travel),
+  // this rank's own blocks last (the peers' partials for them have arrived by then).
   auto tile_coords = [&](int tile, int& m_blk, int& n_blk, int& owner) {
-    if (!gathered) {
+    if (!fused) {
       m_blk = tile % tiles_m;
       n_blk = tile / tiles_m;
       owner = fc.rank;
@@ -457,7 +585,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     n_blk = tile % tiles_n;
     const int tpc = fc.shard_len / kBM;           // m tiles per (batch, owner) chunk
     const int nb = M / fc.seq_len;
-    const int k = i_m / (nb * tpc);
+    const int k = i_m / (nb * tpc) + (gathered ? 0 : 1);
     const int rem = i_m % (nb * tpc);
     owner = (fc.rank + k) % fc.n_ranks;
     m_blk = ((rem / tpc) * fc.seq_len + owner * fc.shard_len) / kBM + rem % tpc;
@@ -471,9 +599,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
+      mbar_init(&tile_done[b], 8);
     }
     *abort_flag = 0;
+    *epoch_slot = fused ? fc.sync[0] + 1 : 0;
+    if (reducing) {
+      uint32_t last = *fc.rs_last[0];
+      if (fc.rs_last[1] != nullptr && static_cast<int32_t>(*fc.rs_last[1] - last) > 0) last = *fc.rs_last[1];
+      *need_slot = last + 1;
+    }
     fence_mbar_init();
+  }
+  if (reducing && blockIdx.x == 0 && threadIdx.x < fc.n_ranks && static_cast<int>(threadIdx.x) != fc.rank) {
+    // everything earlier in this rank's stream is complete: peers may reuse my buffers
+    st_release_sys(fc.rs_started[threadIdx.x] + fc.rank, fc.sync[0] + 1);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -492,8 +631,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      uint32_t ag_epoch = 0;
-      if (gathered) ag_epoch = fc.epochs[fc.channel * kMaxBlocks + 0] + 1;
+      const uint32_t ag_epoch = *epoch_slot;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += n_gemm_ctas) {
         int m_blk, n_blk, owner;
         tile_coords(tile, m_blk, n_blk, owner);
@@ -587,12 +725,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // ------------------------------------------------------------ epilogue --
     const int quad = warp & 3;          // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;   // which half of the tile's columns this warp drains
+    const uint32_t epoch = *epoch_slot;
     int local = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += n_gemm_ctas, ++local) {
+    int first_tile = blockIdx.x;
+    if (reducing) {
+      // peers' buffers are free for this launch once they have got far enough (see FusedComm)
+      bool ok = true;
+      if (lane < fc.n_ranks && lane != fc.rank)
+        ok = wait_flag_sys(fc.rs_started[fc.rank] + lane, *need_slot, fc.budget);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) {
+          report_status(status, kPeerTimeout, 11);
+          *abort_flag = 1;
+        }
+        first_tile = num_tiles;
+      }
+    }
+    for (int tile = first_tile; tile < num_tiles; tile += n_gemm_ctas, ++local) {
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      int m_blk, n_blk, owner_unused;
-      tile_coords(tile, m_blk, n_blk, owner_unused);
+      int m_blk, n_blk, owner;
+      tile_coords(tile, m_blk, n_blk, owner);
       const int m0 = m_blk * kBM;
       const int n0 = n_blk * BN;
       if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag, status, 4)) break;
@@ -600,10 +753,52 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
-      epilogue_columns<BN>(ep, fc, t_row, row, row_ok, n0, half, N);
+      if (!reducing) {
+        epilogue_columns<BN>(ep, fc, t_row, row, row_ok, n0, half, N);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        continue;
+      }
+      if constexpr (FUSED) {
+      const bool own = owner == fc.rank;
+      const int ftile = (row_local(fc, m0) / kBM) * tiles_n + n_blk;
+      if (own) {
+        // the peers computed this tile first: their partials are normally here already
+        bool ok = true;
+        if (lane < fc.n_ranks && lane != fc.rank)
+          ok = wait_flag_sys(fused_flag(fc, fc.rank, 0, ftile, lane), epoch, fc.budget);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) {
+            report_status(status, kPeerTimeout, 8);
+            *abort_flag = 1;
+          }
+          break;
+        }
+      }
+      epilogue_columns_reduce<BN>(ep, fc, t_row, m0, quad, lane, owner, n0, half, N, own,
+                                  reinterpret_cast<uint4*>(smem + L::kTotal) + (warp - 2) * 256);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (lane == 0) {
+        mbar_arrive(&acc_empty[buf]);
+        mbar_arrive(&tile_done[buf]);
+      }
+      // One warp (a different one every tile) publishes the tile once all eight
+      // have stored their part: a single system-scope fence + flag per tile.
+      if (warp == 2 + (local & 7) && (!own || fc.rs_mode == 2)) {
+        bool ok = true;
+        if (lane == 0) ok = mbar_wait(&tile_done[buf], acc_phase, abort_flag, status, 9);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        if (lane == 0) __threadfence_system();
+        __syncwarp();
+        if (!own) {
+          if (lane == 0) st_release_sys(fused_flag(fc, owner, 0, ftile, fc.rank), epoch);
+        } else if (lane < fc.n_ranks && lane != fc.rank) {
+          st_release_sys(fused_flag(fc, lane, 1, ftile, fc.rank), epoch);
+        }
+      }
+      }  // FUSED
     }
   }
 
@@ -618,7 +813,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-  if (fc.rs_mode != 0 && *abort_flag == 0) reduce_phase(fc, n_gemm_ctas, N, status);
+  if (reducing && fc.rs_mode == 2 && *abort_flag == 0) {
+    // all-reduce: the kernel may only end once the other owners' final tiles
+    // have landed in this rank's output (each CTA checks a share of them)
+    const int per_owner = (fc.rows_per_rank / kBM) * tiles_n;
+    const int total = (fc.n_ranks - 1) * per_owner;
+    const uint32_t epoch = *epoch_slot;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += n_gemm_ctas * blockDim.x) {
+      const int owner = (fc.rank + 1 + i / per_owner) % fc.n_ranks;
+      if (!wait_flag_sys(fused_flag(fc, fc.rank, 1, i % per_owner, owner), epoch, fc.budget)) {
+        report_status(status, kPeerTimeout, 10);
+        break;
+      }
+    }
+  }
+  if (fused) fused_leave(fc, *epoch_slot);
 }
 
 // ---------------------------------------------------------------------------
@@ -929,9 +1138,9 @@ static int launch_gemm_pair(const void* A, int lda, const void* B, int ldb, cons
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_gemm(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
-                       int M, int N, int K, int* status, cudaStream_t stream) {
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED>
+static int launch_gemm_impl(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
+                            int M, int N, int K, int* status, cudaStream_t stream) {
   using L = GemmSmem<BN, STAGES>;
   CUtensorMap ta, tb;
   int rc;
@@ -960,8 +1169,8 @@ static int launch_gemm(const void* A, int lda, const void* B, int ldb, const Gem
   }
   if (rc != 0) return 200 + rc;
 
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>;
-  const int smem_bytes = L::kTotal + 1024;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, FUSED>;
+  const int smem_bytes = L::kTotal + 1024 + (fc.rs_mode != 0 ? kEpiStageBytes : 0);
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (fc.ag_copy_ctas > 0) {
@@ -972,6 +1181,19 @@ static int launch_gemm(const void* A, int lda, const void* B, int ldb, const Gem
   kern<<<grid, kGemmThreads, smem_bytes, stream>>>(ta, tb, ep, fc, M, N, K, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
+                       int M, int N, int K, int* status, cudaStream_t stream) {
+  if (fc.rs_mode != 0 || fc.ag_copy_ctas > 0) {
+    // the fused collectives exist for K-major A only (checked by the caller)
+    if constexpr (!A_MN)
+      return launch_gemm_impl<BN, STAGES, A_MN, B_MN, true>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
+    else
+      return kBadArgument;
+  }
+  return launch_gemm_impl<BN, STAGES, A_MN, B_MN, false>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
 }
 
 template <bool A_MN, bool B_MN>
@@ -992,20 +1214,25 @@ static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const G
   return launch_gemm<128, 6, A_MN, B_MN>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
 }
 
-__global__ void epoch_advance_kernel(uint32_t* epoch, uint32_t by) { *epoch += by; }
-
-template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int configure_gemm() {
-  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN, STAGES>::kTotal + 1024);
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED>
+static int configure_gemm_impl() {
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, FUSED>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       GemmSmem<BN, STAGES>::kTotal + 1024 + (FUSED ? kEpiStageBytes : 0));
   // Every large kernel of the library asks for the maximum shared-memory
   // carve-out, and so do the communication kernels meant to run beside them: an
   // SM keeps one carve-out at a time, so kernels that prefer different ones
   // cannot share it and would serialise instead of overlapping.
   if (e == cudaSuccess)
-    e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES, A_MN, B_MN>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                             cudaSharedmemCarveoutMaxShared);
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   return e == cudaSuccess ? 0 : 300 + static_cast<int>(e);
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int configure_gemm() {
+  int rc = configure_gemm_impl<BN, STAGES, A_MN, B_MN, false>();
+  if constexpr (!A_MN) rc |= configure_gemm_impl<BN, STAGES, A_MN, B_MN, true>();
+  return rc;
 }
 
 template <bool A_MN, bool B_MN>
@@ -1087,7 +1314,9 @@ static int gemm_entry(const void* A, int lda, int a_mn, const void* B, int ldb, 
         fc.seq_len != fc.shard_len * fc.n_ranks || N % 32 != 0 || out_f32 || accumulate)
       return kBadArgument;
     if (fc.rs_mode != 0 && (bias != nullptr || residual != nullptr || mode != kEpiPlain)) return kBadArgument;
-    if (fc.ag_copy_ctas > 0 && (a_mn || fc.ag_copy_ctas >= sm_count() / 2)) return kBadArgument;
+    if (fc.rs_mode != 0 && (fc.rows_per_rank / kBM) * ((N + 127) / 128) > kMaxFusedTiles) return kTooLarge;
+    if (fc.rs_mode != 0 && fc.ag_copy_ctas > 0) return kBadArgument;  // the two tile orders exclude each other
+    if (fc.ag_copy_ctas > 0 && (a_mn || fc.ag_copy_ctas >= sm_count() / 2 || fc.ag_copy_ctas > 63)) return kBadArgument;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (!a_mn && !b_mn) return dispatch_tile<false, false>(A, lda, B, ldb, ep, fc, M, N, K, status, s);
@@ -1113,21 +1342,17 @@ extern "C" int nmb_gemm_bf16(const void* A, int lda, int a_mn, const void* B, in
 }
 
 // The same GEMM with a collective fused in (see FusedComm).  `comm` has the
-// layout of nmb::FusedComm; after the launch a one-thread kernel advances the
-// channel's epoch counter by two.
+// layout of nmb::FusedComm.  With a fused reduce, `bias` is added by the owner
+// of each row block after the reduction (comm->rs_bias / rs_residual).
 extern "C" int nmb_gemm_bf16_fused(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C,
                                    int ldc, int M, int N, int K, const void* bias, void* aux_out,
                                    int mode, float alpha, const void* comm, int* status, void* stream) {
   const nmb::FusedComm* fc = static_cast<const nmb::FusedComm*>(comm);
-  const bool rs = fc->rs_mode != 0;  // bias / residual are applied by the reduce phase then
-  int rc = gemm_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, rs ? nullptr : bias, nullptr, 0,
-                      rs ? nullptr : aux_out, nullptr, N, rs ? nmb::kEpiPlain : mode, 0, 0, alpha, *fc, status,
-                      stream);
-  if (rc != 0) return rc;
-  nmb::epoch_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
-      fc->epochs + fc->channel * nmb::kMaxBlocks, 2u);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
+  const bool rs = fc->rs_mode != 0;
+  return gemm_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, rs ? nullptr : bias, nullptr, 0,
+                    rs ? nullptr : aux_out, nullptr, N, rs ? nmb::kEpiPlain : mode, 0, 0, alpha, *fc, status, stream);
 }
+
+extern "C" int nmb_fused_max_tiles() { return nmb::kMaxFusedTiles; }
 
 extern "C" int nmb_fused_comm_size() { return static_cast<int>(sizeof(nmb::FusedComm)); }

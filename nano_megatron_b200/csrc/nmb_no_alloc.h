@@ -25,9 +25,14 @@
 //     `nmb_col_reduce(mode = 0)`.
 //   * The caller passes every input and output pointer; the function calls no
 //     cudaMalloc, cudaFree or any other allocating routine.
-//   * cols > NMB_NOALLOC_MAX_COLS (or odd cols / ld) is rejected with a
-//     non-zero code and nothing is launched; `nmb_col_sum_noalloc_strerror`
-//     turns the code into a sentence.
+//   * cols > NMB_NOALLOC_MAX_COLS is rejected with a non-zero code and nothing
+//     is launched; so are odd cols / ld, ld < cols, a `dy` that is not 4-byte
+//     aligned (rows are read two bf16 at a time, so a view that starts at an
+//     odd element of a wider row is refused rather than read misaligned) and an
+//     `out` that is not 2-byte aligned.  `nmb_col_sum_noalloc_strerror` turns
+//     the code into a sentence.
+//   * rows == 0 is a sum over nothing: out is zeroed (left alone when
+//     accumulating); cols == 0 does nothing.
 //   * The first call on each device looks up the device address of the
 //     scratch array (cudaGetSymbolAddress, with that device current) and caches
 //     it.  Make that first call before starting any stream capture on the
@@ -47,7 +52,7 @@ extern "C" {
 
 enum {
   NMB_NOALLOC_OK = 0,
-  NMB_NOALLOC_BAD_SHAPE = 3,   // cols or ld odd, or a null pointer
+  NMB_NOALLOC_BAD_SHAPE = 3,   // cols or ld odd, ld < cols, dy not 4-byte / out not 2-byte aligned, null pointer
   NMB_NOALLOC_TOO_LARGE = 4,   // cols > NMB_NOALLOC_MAX_COLS
   NMB_NOALLOC_NO_SCRATCH = 5,  // the scratch symbol could not be resolved on this device
 };

@@ -119,13 +119,15 @@ class DistributedDataParallel(nn.Module):
             dtype, device = b.params[0].dtype, b.params[0].device
             flat = None
             if ws is not None and self._sync_group_size > 1:
-                flat = ws.alloc_tensor(b.numel(), dtype)
-                if flat is not None:
-                    b.fused_reduce = ws.make_allreduce_mean(flat)
+                # padded to whole 16-byte vectors so the peer kernel takes every bucket
+                per = 16 // torch.empty((), dtype=dtype).element_size()
+                padded = ws.alloc_tensor((b.numel() + per - 1) // per * per, dtype)
+                if padded is not None:
+                    padded.zero_()
+                    b.fused_reduce = ws.make_allreduce_mean(padded)
+                    flat = padded[: b.numel()]
             if flat is None:
                 flat = torch.zeros(b.numel(), dtype=dtype, device=device)
-            else:
-                flat.zero_()
             b.bind_persistent(flat)
             self._flat_buffers.append(flat)
 

@@ -30,10 +30,12 @@ CHANNEL_TP, CHANNEL_DP, CHANNEL_CP, CHANNEL_AUX = 0, 1, 2, 3
 # with that many blocks (it shares SMs with the backward GEMMs instead of taking
 # them over); positive: the latency-first kernel.
 DDP_ALLREDUCE_BLOCKS = int(os.environ.get("NMB_DDP_AR_BLOCKS", "-148"))
-# Optional arena: with NMB_SYMM_ARENA_MB=<n> tensors up to n MiB are carved out
-# of shared n-MiB symmetric allocations (one IPC handle and one handle exchange
-# per arena instead of per tensor).  Off (0) by default.
-ARENA_BYTES = int(os.environ.get("NMB_SYMM_ARENA_MB", "0")) << 20
+# Arena: tensors up to NMB_SYMM_ARENA_MB MiB (default 256, 0 = off) are carved
+# out of shared symmetric allocations of that size: one IPC handle, one handle
+# exchange and, at teardown, one unmap per peer per arena instead of per tensor
+# (a model has hundreds of symmetric tensors; unmapping them one by one from
+# seven peers made the teardown of an 8-rank job take minutes).
+ARENA_BYTES = int(os.environ.get("NMB_SYMM_ARENA_MB", "256")) << 20
 
 
 class _RawCuda:
@@ -142,7 +144,13 @@ class SymmetricWorkspace:
             self._arena_used += step
         else:
             alloc, off = self._alloc_raw(nbytes), 0
-        t = alloc.bytes[off: off + nbytes].view(dtype)
+        if off == 0 and nbytes == alloc.nbytes:
+            t = alloc.bytes.view(dtype)
+        else:
+            # A tensor of its own (not a view of the arena): tensors carved from one
+            # arena must not share an autograd version counter, or an in-place
+            # write to one would invalidate every other one saved for backward.
+            t = torch.as_tensor(_RawCuda(alloc.local_ptr + off, nbytes), device=self.device).view(dtype)
         self._by_ptr[t.data_ptr()] = (alloc, off)
         return t
 
@@ -214,29 +222,41 @@ class SymmetricWorkspace:
         return dst.view(self.size, *src.shape)
 
     def embedding_scatter(self, ids: torch.Tensor, positions: Optional[torch.Tensor], tok_w: torch.Tensor,
-                          pos_w: Optional[torch.Tensor], out: torch.Tensor, vocab_start: int, seq_len: int) -> None:
+                          pos_w: Optional[torch.Tensor], out: torch.Tensor, vocab_start: int, seq_len: int,
+                          *, to_all: bool = False) -> None:
         """Every token row owned by this rank's vocabulary shard is written (token +
         position embedding) into the sequence-shard owner's ``out`` (symmetric,
-        ``[B * S/size, H]``)."""
+        ``[B * S/size, H]``) or, with ``to_all``, into every rank's ``out``
+        (``[B * S, H]``)."""
         n_tokens = ids.numel()
         rc = native.lib().nmb_embedding_scatter(
             native.ptr(ids), native.ptr(positions), native.ptr(tok_w), native.ptr(pos_w), self.peer_table(out),
             ctypes.c_int(self.size), ctypes.c_int(n_tokens), ctypes.c_int(tok_w.shape[1]), ctypes.c_int(vocab_start),
-            ctypes.c_int(tok_w.shape[0]), ctypes.c_int(seq_len), ctypes.c_int(seq_len // self.size),
-            native.stream_ptr(self.device))
+            ctypes.c_int(tok_w.shape[0]), ctypes.c_int(seq_len), ctypes.c_int(max(seq_len // self.size, 1)),
+            ctypes.c_int(int(to_all)), native.stream_ptr(self.device))
         native.check_rc(rc, "nmb_embedding_scatter")
 
+    def allocated_bytes(self) -> int:
+        """Device memory held by this workspace on this rank."""
+        return sum(a.nbytes for a in self._allocs)
+
     def make_allreduce_mean(self, flat: torch.Tensor) -> Callable[[torch.Tensor, int], bool]:
-        """Reducer for a DDP bucket whose buffer is ``flat`` (see ``GradBucket.fused_reduce``)."""
+        """Reducer for a DDP bucket whose gradients live at the start of ``flat``
+        (see ``GradBucket.fused_reduce``).  ``flat`` is the whole symmetric
+        allocation, padded to a multiple of 16 bytes, so every bucket size can
+        be reduced by the kernel and no call falls back to the library path."""
         per = 8 if flat.dtype == torch.bfloat16 else 4
+        if flat.numel() % per != 0:
+            raise ValueError("bucket buffer must be padded to a multiple of 16 bytes")
         table, pads = self.peer_table(flat), self.pad.table()
+        numel, is_bf16 = flat.numel(), int(flat.dtype == torch.bfloat16)
 
         def reduce(buf: torch.Tensor, divisor: int) -> bool:
-            if buf.data_ptr() != flat.data_ptr() or buf.numel() % per != 0:
+            if buf.data_ptr() != flat.data_ptr() or buf.numel() > numel:
                 return False
             rc = native.lib().nmb_allreduce_scale(
                 table, pads, native.ptr(self.epochs), ctypes.c_int(CHANNEL_DP), ctypes.c_int(self.rank),
-                ctypes.c_int(self.size), ctypes.c_longlong(buf.numel()), ctypes.c_int(int(buf.dtype == torch.bfloat16)),
+                ctypes.c_int(self.size), ctypes.c_longlong(numel), ctypes.c_int(is_bf16),
                 ctypes.c_float(1.0 / divisor), ctypes.c_int(DDP_ALLREDUCE_BLOCKS), native.ptr(self.status),
                 ctypes.c_longlong(self.budget), native.stream_ptr(self.device))
             native.check_rc(rc, "nmb_allreduce_scale")
@@ -259,5 +279,5 @@ def enable_symmetric_memory(ctx: Any) -> dict[str, SymmetricWorkspace]:
             symmetric.register_workspace(group, ws)
             made[name] = ws
     from ..ops import fused_tp
-    fused_tp.ENABLED = ctx.pipeline_parallel_size == 1
+    fused_tp.ENABLED = True
     return made

@@ -10,25 +10,45 @@ from .symm_mem import CHANNEL_CP, SymmetricWorkspace
 
 
 class _KVExchange:
-    """Per-workspace pool of symmetric K/V slots (one pair per attention call of
-    a forward pass, reused every step) and one dK/dV staging area."""
+    """Per-workspace pool of symmetric K/V slots and one dK/dV staging area.
+
+    A slot pair is leased by an attention call that will run a backward pass
+    and stays taken until that backward has run (or its autograd graph is
+    dropped): the backward re-reads K/V from the slot -- its own and, through
+    peer pointers, the other ranks'.  Slots are handed out in call order and the
+    order restarts with every forward pass when nothing is outstanding, so in
+    the steady state every layer gets the same slot every step; with several
+    forward passes outstanding (microbatches, an evaluation pass between
+    forward and backward) later passes get further slots instead of overwriting
+    K/V that a pending backward still needs.  All ranks of the group make the
+    same calls in the same order, so their slot choices agree.
+    """
 
     def __init__(self, ws: SymmetricWorkspace) -> None:
         self.ws = ws
         self.slots: list[tuple[Tensor, Tensor]] = []
+        self.leased: list[bool] = []
         self.cursor = 0
         self.staging: dict[tuple, tuple[Tensor, Tensor]] = {}
 
-    def next_slot(self, like: Tensor) -> tuple[Tensor, Tensor]:
+    def next_slot(self, like: Tensor, lease: bool) -> tuple[int, tuple[Tensor, Tensor]]:
+        while self.cursor < len(self.slots) and self.leased[self.cursor]:
+            self.cursor += 1
         if self.cursor == len(self.slots):
             k = self.ws.alloc_tensor(like.numel(), like.dtype).view(like.shape)
             v = self.ws.alloc_tensor(like.numel(), like.dtype).view(like.shape)
             self.slots.append((k, v))
-        pair = self.slots[self.cursor]
+            self.leased.append(False)
+        index = self.cursor
+        pair = self.slots[index]
         if pair[0].shape != like.shape:
             raise RuntimeError("context-parallel K/V shape changed between steps")
+        self.leased[index] = lease
         self.cursor += 1
-        return pair
+        return index, pair
+
+    def release(self, index: int) -> None:
+        self.leased[index] = False
 
     def stage(self, like: Tensor) -> tuple[Tensor, Tensor]:
         key = (tuple(like.shape), like.dtype)
@@ -40,6 +60,21 @@ class _KVExchange:
         return self.staging[key]
 
 
+class _SlotLease:
+    """Gives a K/V slot back when the attention call's autograd context goes away."""
+
+    def __init__(self, ex: _KVExchange, index: int) -> None:
+        self.ex, self.index = ex, index
+
+    def release(self) -> None:
+        if self.ex is not None:
+            self.ex.release(self.index)
+            self.ex = None
+
+    def __del__(self) -> None:
+        self.release()
+
+
 def _exchange(ws: SymmetricWorkspace) -> _KVExchange:
     ex = getattr(ws, "_kv_exchange", None)
     if ex is None:
@@ -49,7 +84,8 @@ def _exchange(ws: SymmetricWorkspace) -> _KVExchange:
 
 
 def begin_step(ws: SymmetricWorkspace) -> None:
-    """Rewind the K/V slot cursor (called at the start of every forward pass)."""
+    """Restart the K/V slot order (called at the start of every forward pass);
+    slots still leased by a pending backward are skipped."""
     _exchange(ws).cursor = 0
 
 
@@ -70,7 +106,11 @@ class _CPFlashPeer(torch.autograd.Function):
         from ..ops.attention import attn_fwd
 
         ex = _exchange(ws)
-        k_slot, v_slot = ex.next_slot(k)
+        # Inside a CUDA graph capture forward and backward of the step are recorded
+        # together and replayed as a unit: nothing stays outstanding, no lease.
+        lease = any(ctx.needs_input_grad[:3]) and not torch.cuda.is_current_stream_capturing()
+        index, (k_slot, v_slot) = ex.next_slot(k, lease=lease)
+        ctx.lease = _SlotLease(ex, index) if lease else None
         k_slot.copy_(k)
         v_slot.copy_(v)
         ws.barrier(CHANNEL_CP)                       # every rank's K/V is published
@@ -102,6 +142,8 @@ class _CPFlashPeer(torch.autograd.Function):
         ws.barrier(CHANNEL_CP)                       # all contributions have landed
         dk = dk_stage[cp_rank:].float().sum(0).to(k_slot.dtype)
         dv = dv_stage[cp_rank:].float().sum(0).to(v_slot.dtype)
+        if ctx.lease is not None:
+            ctx.lease.release()
         return dq, dk, dv, None, None, None, None
 
 
@@ -128,8 +170,10 @@ class _SPEmbeddingFn(torch.autograd.Function):
         b, s = ids.shape
         h = tok_w.shape[1]
         rows = b * s // ws.size
+        # one buffer per shape: the result is copied out below, and every rank
+        # passes the leading barrier only when all are done with the previous use
         cache = ws.__dict__.setdefault("_emb_out", {})
-        key = (id(site), rows, h)
+        key = ("sp", rows, h)
         if key not in cache:
             cache[key] = ws.alloc_tensor(rows * h, tok_w.dtype).view(rows, h)
         out = cache[key]
@@ -181,3 +225,44 @@ class _SPEmbeddingFn(torch.autograd.Function):
 def sp_embedding(ids: Tensor, positions, tok_w: Tensor, pos_w, vocab_start: int, ws: SymmetricWorkspace,
                  site: Any) -> Tensor:
     return _SPEmbeddingFn.apply(ids, positions, tok_w, pos_w, vocab_start, ws, site)
+
+
+class _TPEmbeddingFn(torch.autograd.Function):
+    """Vocabulary-parallel embedding with a replicated ``[B, S, H]`` output
+    (tensor parallelism without sequence parallelism).
+
+    The reference sums the ranks' masked lookups with an all-reduce
+    (nano_megatron/parallel/vocab_parallel.py:86-100).  Every row has exactly one
+    non-zero contributor, so the owner of a token's vocabulary id writes the row
+    (token + position embedding) into every rank's buffer instead -- no
+    arithmetic, one pass.  Backward is local: the output gradient is replicated
+    and each rank scatter-adds the rows of its own vocabulary shard.
+    """
+
+    @staticmethod
+    def forward(ctx: Any, ids: Tensor, positions, tok_w: Tensor, pos_w, vocab_start: int, ws: SymmetricWorkspace):
+        b, s = ids.shape
+        h = tok_w.shape[1]
+        cache = ws.__dict__.setdefault("_emb_out", {})
+        key = ("all", b * s, h)
+        if key not in cache:
+            cache[key] = ws.alloc_tensor(b * s * h, tok_w.dtype).view(b * s, h)
+        out = cache[key]
+        ids_c = ids.contiguous()
+        pos_c = positions.contiguous() if positions is not None else None
+        ws.barrier()                      # every rank has copied the previous result out
+        ws.embedding_scatter(ids_c, pos_c, tok_w, pos_w, out, vocab_start, s, to_all=True)
+        ws.barrier()                      # every row has been written by its owner
+        ctx.save_for_backward(ids_c, pos_c)
+        ctx.params = (tok_w, pos_w)
+        ctx.vocab_start = vocab_start
+        return out.view(b, s, h).clone()
+
+    @staticmethod
+    def backward(ctx: Any, dy: Tensor):
+        from ..ops.functional import _EmbeddingFn
+        return (*_EmbeddingFn.backward(ctx, dy), None)
+
+
+def tp_embedding(ids: Tensor, positions, tok_w: Tensor, pos_w, vocab_start: int, ws: SymmetricWorkspace) -> Tensor:
+    return _TPEmbeddingFn.apply(ids, positions if pos_w is not None else None, tok_w, pos_w, vocab_start, ws)

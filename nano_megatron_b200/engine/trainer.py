@@ -8,6 +8,8 @@ parallel paths are driven by hand-written loops in the benchmark scripts
 
     trainer = Trainer(model, ctx, lr=1e-4)
     loss = trainer.step(input_ids)          # zero-grad, fwd, loss, bwd, grad sync, AdamW
+    loss = trainer.forward_backward(ids)    # the same without the optimizer (the reference's
+                                            # benchmark step, scripts/benchmark_tp.py:182-186)
 
 On CUDA the step (all kernels, the NCCL or peer-memory gradient reductions and
 the optimizer) is captured once into a CUDA graph after a few eager warm-up
@@ -47,14 +49,18 @@ class Trainer:
             # package are plain kernels and capture like any other.
             self._want_graph = False
             self.graph_error = "not captured: the step contains NCCL collectives"
-        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        #: captured step graphs, keyed by "with optimizer update?"
+        self._graphs: dict[bool, torch.cuda.CUDAGraph] = {}
+        self._tried: set[bool] = set()
+        self._pool = None
         self._graph_warmup = graph_warmup
-        self._eager_steps = 0
+        self._eager_steps = {True: 0, False: 0}
         self._ids: Optional[Tensor] = None
         self._labels: Optional[Tensor] = None
-        self._loss: Optional[Tensor] = None
+        self._loss_out: Optional[Tensor] = None
         #: number of this library's kernels recorded in the captured graph
         self.kernels_in_graph = 0
+        self.kernels_in_graphs: dict[bool, int] = {}
 
     def _collectives_are_graph_safe(self) -> bool:
         ctx = self.ctx
@@ -63,11 +69,10 @@ class Trainer:
         if ctx.pipeline_parallel_size > 1:
             return False
         if ctx.tensor_parallel_size > 1:
-            # sequence-parallel TP with every collective on peer-memory kernels
+            # every TP collective (with or without sequence parallelism) on peer-memory kernels
             from ..distributed import symmetric
             from ..ops import fused_tp
-            if not (ctx.sequence_parallel and fused_tp.ENABLED
-                    and symmetric.workspace_for(ctx.tensor_parallel_group) is not None):
+            if not (fused_tp.ENABLED and symmetric.workspace_for(ctx.tensor_parallel_group) is not None):
                 return False
         if ctx.context_parallel_size > 1:
             from ..distributed import symmetric
@@ -78,7 +83,7 @@ class Trainer:
         return all(b.fused_reduce is not None for b in self.ddp._buckets)
 
     # ------------------------------------------------------------------ step --
-    def _step_body(self) -> Tensor:
+    def _step_body(self, with_optimizer: bool = True) -> Tensor:
         with nvtx_range("zero_grad"):
             self.ddp.zero_grad()
         with nvtx_range("forward"):
@@ -88,51 +93,79 @@ class Trainer:
             loss.backward()
         with nvtx_range("grad_sync"):
             self.ddp.finish_grad_sync()
-        with nvtx_range("optimizer"):
-            self.optimizer.step()
-        return loss.detach()
+        if with_optimizer:
+            with nvtx_range("optimizer"):
+                self.optimizer.step()
+        # The loss is handed out in a buffer of its own so that replaying one
+        # captured graph never overwrites the value returned by the other.
+        self._loss_out.copy_(loss.detach())
+        return self._loss_out
 
     def _load(self, input_ids: Tensor, labels: Optional[Tensor]) -> None:
         if self._ids is None:
             self._ids = torch.empty(input_ids.shape, dtype=torch.long, device=self.device)
             self._labels = torch.empty(input_ids.shape, dtype=torch.long, device=self.device)
+            self._loss_out = torch.zeros((), dtype=torch.float32, device=self.device)
         self._ids.copy_(input_ids, non_blocking=True)
         self._labels.copy_(input_ids if labels is None else labels, non_blocking=True)
 
     def step(self, input_ids: Tensor, labels: Optional[Tensor] = None) -> Tensor:
         """One optimisation step; returns the (device) scalar loss."""
-        self._load(input_ids, labels)
-        if self._graph is not None:
-            self._graph.replay()
-            return self._loss
-        if self._want_graph and self._eager_steps >= self._graph_warmup:
-            self._capture()
-            if self._graph is not None:
-                self._graph.replay()
-                return self._loss
-        self._eager_steps += 1
-        return self._step_body()
+        return self._run(input_ids, labels, True)
 
-    def _capture(self) -> None:
-        """Capture the whole step.  A failure leaves the trainer in eager mode
-        (``graph_error`` says why)."""
-        self._want_graph = False
+    def forward_backward(self, input_ids: Tensor, labels: Optional[Tensor] = None) -> Tensor:
+        """Zero-grad, forward, loss, backward and gradient synchronisation, no
+        parameter update: gradients are left in ``.grad`` for the caller."""
+        return self._run(input_ids, labels, False)
+
+    def _run(self, input_ids: Tensor, labels: Optional[Tensor], with_optimizer: bool) -> Tensor:
+        self._load(input_ids, labels)
+        graph = self._graphs.get(with_optimizer)
+        if graph is None and self._want_graph and with_optimizer not in self._tried \
+                and self._eager_steps[with_optimizer] >= self._graph_warmup:
+            graph = self._capture(with_optimizer)
+        if graph is not None:
+            if with_optimizer:
+                self.optimizer.sync_hyper()      # a changed lr reaches the device outside the graph
+            graph.replay()
+            return self._loss_out
+        self._eager_steps[with_optimizer] += 1
+        return self._step_body(with_optimizer)
+
+    def _capture(self, with_optimizer: bool) -> Optional[torch.cuda.CUDAGraph]:
+        """Capture the whole step.  A failure leaves that kind of step in eager
+        mode (``graph_error`` says why)."""
+        self._tried.add(with_optimizer)
         torch.cuda.synchronize(self.device)
         try:
             graph = torch.cuda.CUDAGraph()
             before = native.launches
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                self._loss = self._step_body()
-            self.kernels_in_graph = native.launches - before
-            self._graph = graph
+            kwargs = {} if self._pool is None else {"pool": self._pool}
+            with torch.cuda.graph(graph, capture_error_mode="thread_local", **kwargs):
+                self._step_body(with_optimizer)
+            if self._pool is None:
+                self._pool = graph.pool()
+            if with_optimizer or not self.kernels_in_graph:
+                self.kernels_in_graph = native.launches - before
+            self.kernels_in_graphs[with_optimizer] = native.launches - before
+            self._graphs[with_optimizer] = graph
+            return graph
         except Exception as exc:  # pragma: no cover - depends on the device
             self.graph_error = f"{type(exc).__name__}: {exc}"
-            self._graph = None
             torch.cuda.synchronize(self.device)
+            return None
+
+    def reset_graphs(self) -> None:
+        """Drop the captured graphs (they are re-captured after the usual eager
+        warm-up).  Needed after anything that moves a tensor the graphs address:
+        re-created optimizer state, re-bound gradient buffers."""
+        self._graphs.clear()
+        self._tried.clear()
+        self._eager_steps = {True: 0, False: 0}
 
     @property
     def graphed(self) -> bool:
-        return self._graph is not None
+        return bool(self._graphs)
 
     def check(self) -> None:
         """Raise if any kernel reported a device-side failure (host sync)."""

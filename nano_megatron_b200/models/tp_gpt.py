@@ -357,6 +357,14 @@ class TPGPT(nn.Module):
             if pos_w is not None:
                 x = x + torch.nn.functional.embedding(positions, pos_w)
             return x, positions
+        if self._tp_size > 1 and OF.use_native(self.tok_emb.weight) and self.tok_emb.weight.shape[1] % 8 == 0:
+            from ..distributed import symmetric
+            ws = symmetric.workspace_for(self._tp_group)
+            if ws is not None:
+                # the owner of each token's vocabulary id writes the row to every rank (no all-reduce)
+                from ..distributed.symm_ops import tp_embedding
+                return tp_embedding(input_ids, positions, self.tok_emb.weight, pos_w, self.vocab_start_index,
+                                    ws), positions
         x = self.tok_emb(input_ids, positions=positions, pos_weight=pos_w)
         return x, positions
 

@@ -45,11 +45,15 @@ class FusedAdamWPlan:
         self._hyper_host: tuple | None = None
         self._keep = (params, states)
 
-    def step(self, lr: float, betas: tuple[float, float], eps: float, weight_decay: float) -> None:
+    def set_hyper(self, lr: float, betas: tuple[float, float], eps: float, weight_decay: float) -> None:
+        """Refresh the device copy of the hyper-parameters if they changed."""
         hv = (lr, betas[0], betas[1], eps, weight_decay)
         if hv != self._hyper_host:
             self.hyper.copy_(torch.tensor(hv, dtype=torch.float32))
             self._hyper_host = hv
+
+    def step(self, lr: float, betas: tuple[float, float], eps: float, weight_decay: float) -> None:
+        self.set_hyper(lr, betas, eps, weight_decay)
         rc = native.lib().nmb_adamw_step(native.ptr(self.table), ctypes.c_int(self.n),
                                          ctypes.c_longlong(self.total_blocks), native.ptr(self.hyper),
                                          native.ptr(self.step_count), native.stream_ptr(self.table.device))

@@ -399,6 +399,22 @@ def embedding(ids: Tensor, positions: Optional[Tensor], tok_w: Tensor, pos_w: Op
 
 
 # ----------------------------------------------------------- cross entropy --
+_CE_EXCHANGES: dict[tuple, "kernels.CeExchange"] = {}
+
+
+def _ce_exchange(rows: int, device: torch.device, ws: Any) -> "kernels.CeExchange":
+    """Exchange buffers per row count, kept on the workspace (tensor parallel;
+    creating them is a collective over its group, like every symmetric
+    allocation) or per device (single rank)."""
+    cache = _CE_EXCHANGES if ws is None else ws.__dict__.setdefault("_ce_exchanges", {})
+    key = (device.index, rows)
+    ex = cache.get(key)
+    if ex is None:
+        ex = kernels.CeExchange(rows, device, ws)
+        cache[key] = ex
+    return ex
+
+
 class _CrossEntropyFn(torch.autograd.Function):
     """Sum of token losses and number of valid tokens over vocabulary-sharded logits."""
 
@@ -406,18 +422,19 @@ class _CrossEntropyFn(torch.autograd.Function):
     def forward(ctx, logits: Tensor, target: Tensor, vocab_start: int, ignore_index: int, group: Any,
                 backend: Any, tp_size: int, inplace_backward: bool):
         target = target.contiguous()
-        stats = kernels.ce_stats(logits, target, vocab_start)
+        ws = None
         if tp_size > 1:
             from ..distributed import symmetric
             ws = symmetric.workspace_for(group)
-            if ws is not None and (stats.numel() * 4) % 16 == 0:
-                gathered = ws.all_gather(stats)             # peer stores, graph-capturable
-            else:
-                gathered = torch.empty((tp_size, *stats.shape), dtype=stats.dtype, device=stats.device)
-                backend.all_gather_into_tensor(gathered.view(-1, stats.shape[-1]), stats, group=group)
+        if tp_size == 1 or ws is not None:
+            # ONE launch: statistics, exchange of the triples through peer memory, combine
+            lse, accum = kernels.ce_forward_fused(logits, target, vocab_start, ignore_index,
+                                                  _ce_exchange(logits.shape[0], logits.device, ws))
         else:
-            gathered = stats.unsqueeze(0)
-        lse, accum, _ = kernels.ce_combine(gathered, target, ignore_index)
+            stats = kernels.ce_stats(logits, target, vocab_start)
+            gathered = torch.empty((tp_size, *stats.shape), dtype=stats.dtype, device=stats.device)
+            backend.all_gather_into_tensor(gathered.view(-1, stats.shape[-1]), stats, group=group)
+            lse, accum, _ = kernels.ce_combine(gathered, target, ignore_index)
         ctx.save_for_backward(logits, target, lse)
         ctx.meta = (vocab_start, ignore_index, inplace_backward)
         loss_sum, count = accum[0], accum[1]

@@ -138,6 +138,62 @@ def ce_combine(all_stats: torch.Tensor, target: torch.Tensor, ignore_index: int,
     return lse, accum, loss_rows
 
 
+class _CeComm(ctypes.Structure):
+    _fields_ = [("gathered", (ctypes.c_void_p * 8) * 2), ("flags", ctypes.c_void_p * 8), ("sync", ctypes.c_void_p),
+                ("rank", c_int), ("n_ranks", c_int), ("budget", c_ll)]
+
+
+class CeExchange:
+    """Buffers of the one-launch cross-entropy forward for a given row count:
+    two gather buffers of (max, sum-exp, target logit) triples per rank and row,
+    the peers' "all rows stored" flags and the device-side epoch.  With a
+    symmetric workspace ``ws`` the buffers are peer-addressable (tensor
+    parallelism); without one they are plain local tensors (single rank)."""
+
+    def __init__(self, rows: int, device: torch.device, ws=None) -> None:
+        assert native.lib().nmb_ce_comm_size() == ctypes.sizeof(_CeComm), "CeComm layout mismatch"
+        self.rows, self.ws = rows, ws
+        n = ws.size if ws is not None else 1
+        self.sync = torch.zeros(2, dtype=torch.int32, device=device)
+        self.comm = _CeComm()
+        self._keep = []
+        if ws is None:
+            for parity in range(2):
+                buf = torch.empty(rows * 4, dtype=torch.float32, device=device)
+                self._keep.append(buf)
+                self.comm.gathered[parity][0] = buf.data_ptr()
+            self.comm.rank, self.comm.n_ranks, self.comm.budget = 0, 1, 0
+        else:
+            flags = ws.alloc_tensor(8, torch.int32)
+            self._keep.append(flags)
+            for i, p in enumerate(ws.peers_of(flags)):
+                self.comm.flags[i] = p
+            for parity in range(2):
+                buf = ws.alloc_tensor(n * rows * 4, torch.float32)
+                self._keep.append(buf)
+                for i, p in enumerate(ws.peers_of(buf)):
+                    self.comm.gathered[parity][i] = p
+            self.comm.rank, self.comm.n_ranks, self.comm.budget = ws.rank, n, ws.budget
+        self.comm.sync = self.sync.data_ptr()
+
+
+def ce_forward_fused(logits: torch.Tensor, target: torch.Tensor, vocab_start: int, ignore_index: int,
+                     ex: CeExchange):
+    """One launch: per-row statistics, cross-rank exchange, combine.  Returns
+    ``(lse[rows], accum[2] = {loss sum, valid count})``."""
+    assert logits.dim() == 2 and logits.stride(1) == 1 and logits.dtype == torch.bfloat16
+    rows, vloc = logits.shape
+    assert rows == ex.rows
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    accum = torch.empty(2, dtype=torch.float32, device=logits.device)
+    rc = native.lib().nmb_ce_forward_fused(
+        native.ptr(logits), c_ll(logits.stride(0)), native.ptr(target), c_int(vocab_start), c_int(vloc),
+        c_int(ignore_index), ctypes.byref(ex.comm), native.ptr(lse), native.ptr(accum), c_int(rows),
+        native.ptr(native.status_word(logits.device)), native.stream_ptr(logits.device))
+    native.check_rc(rc, "nmb_ce_forward_fused")
+    return lse, accum
+
+
 def ce_bwd(logits, target, vocab_start: int, ignore_index: int, lse, gscale, out: Optional[torch.Tensor] = None):
     rows, vloc = logits.shape
     if out is None:

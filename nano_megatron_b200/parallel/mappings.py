@@ -340,6 +340,16 @@ class ColumnParallelLinear(nn.Module):
                 if split_gelu:
                     return out
                 return out[1] if gelu else out
+        if not self.sequence_parallel and self.tp_size > 1 and OF.native_linear_ok(x, self.weight):
+            from ..ops import fused_tp
+            st = fused_tp.tp_fused_for(self.group) if fused_tp.ENABLED else None
+            rows = x.numel() // x.shape[-1]
+            if st is not None and st.all_reduce_supported(rows, x.shape[-1]):
+                # local GEMM; the all-reduce of the input gradient rides in the dgrad GEMM
+                out = fused_tp._TPColumnLinearFn.apply(x, self.weight, self.bias, st, split_gelu or gelu)
+                if split_gelu:
+                    return out
+                return out[1] if gelu else out
         if self.sequence_parallel:
             x = gather_from_sequence_parallel_region(x, self.group, self.backend, self.tp_rank, self.tp_size)
         elif self.tp_size > 1:
@@ -385,6 +395,14 @@ class RowParallelLinear(nn.Module):
                 # GEMM with the reduce-scatter (and bias / residual) fused in
                 return fused_tp._SPRowLinearFn.apply(x, self.weight, self.bias, residual,
                                                      gelu_pre if fused else None, st, x.shape[1])
+        if not self.sequence_parallel and OF.native_linear_ok(x, self.weight):
+            from ..ops import fused_tp
+            st = fused_tp.tp_fused_for(self.group) if fused_tp.ENABLED else None
+            rows = x.numel() // x.shape[-1]
+            if st is not None and st.all_reduce_supported(rows, self.weight.shape[0]):
+                # GEMM with the all-reduce (and bias / residual) fused in
+                return fused_tp._TPRowLinearFn.apply(x, self.weight, self.bias, residual,
+                                                     gelu_pre if fused else None, st)
         out = OF.linear_from_gelu(gelu_pre, x, self.weight, None) if fused else OF.linear(x, self.weight, None)
         if self.sequence_parallel:
             out = reduce_scatter_to_sequence_parallel_region(out, self.group, self.backend, self.tp_rank, self.tp_size)

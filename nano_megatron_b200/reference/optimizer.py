@@ -128,14 +128,43 @@ class AdamW:
         }
 
     def load_state_dict(self, state: dict[str, dict[str, Any]]) -> None:
+        """Load moments and step counts.  Existing state tensors of matching
+        shape are overwritten *in place* (and the fused plan's device-side step
+        counter with them), so device addresses baked into a captured CUDA
+        graph of the step stay valid and the replayed graph sees the loaded
+        state."""
         by_name = dict(self._params)
         fresh: dict[str, dict[str, Any]] = {}
+        in_place = True
         for n, entry in state.items():
             dev = by_name[n].device if n in by_name else entry["exp_avg"].device
+            old = self.state.get(n)
+            if (old is not None and old["exp_avg"].shape == entry["exp_avg"].shape
+                    and old["exp_avg"].device == torch.device(dev)):
+                old["exp_avg"].copy_(entry["exp_avg"].detach())
+                old["exp_avg_sq"].copy_(entry["exp_avg_sq"].detach())
+                old["step"] = int(entry["step"])
+                fresh[n] = old
+                continue
+            in_place = False
             fresh[n] = {
                 "exp_avg": entry["exp_avg"].detach().to(device=dev, dtype=torch.float32).clone(),
                 "exp_avg_sq": entry["exp_avg_sq"].detach().to(device=dev, dtype=torch.float32).clone(),
                 "step": int(entry["step"]),
             }
+        if set(fresh) != set(self.state):
+            in_place = False
         self.state = fresh
+        if self._fused is not None and in_place:
+            steps = {int(self.state[n]["step"]) for n in self._fused.names}
+            if len(steps) == 1:
+                self._fused.step_count.fill_(steps.pop())
+                return
         self._fused = None
+
+    def sync_hyper(self) -> None:
+        """Push ``lr`` / betas / eps / weight decay to the fused plan's device
+        copy if they changed on the host (a plain device copy; call it outside a
+        captured graph, before replaying it)."""
+        if self._fused is not None:
+            self._fused.set_hyper(self.lr, self.betas, self.eps, self.weight_decay)

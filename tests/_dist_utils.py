@@ -19,7 +19,7 @@ def port_for(test_id: str) -> int:
     return 29500 + int(hashlib.sha1(test_id.encode()).hexdigest(), 16) % 2000
 
 
-def launch(script: str, worker: str, world: int, *, timeout: int = 300, extra_env: dict | None = None) -> None:
+def launch(script: str, worker: str, world: int, *, timeout: int = 300, extra_env: dict | None = None) -> str:
     """Run ``script`` under torchrun with ``world`` ranks; ``worker`` names the function to run."""
     env = dict(os.environ)
     env[WORKER_ENV] = worker
@@ -36,6 +36,7 @@ def launch(script: str, worker: str, world: int, *, timeout: int = 300, extra_en
     if proc.returncode != 0:
         tail = (proc.stdout[-3000:] + "\n" + proc.stderr[-6000:])
         raise AssertionError(f"distributed worker {worker} (world {world}) failed:\n{tail}")
+    return proc.stdout
 
 
 def run_worker_if_requested(namespace: dict) -> None:

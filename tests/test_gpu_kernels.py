@@ -107,6 +107,28 @@ def test_cross_entropy_single_rank(n, v):
     assert (logits.grad.float() - ref_in.grad).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("n,v", [(33, 1000), (130, 50304), (5, 77)])
+def test_one_launch_cross_entropy_forward(n, v):
+    """Statistics + combine in one launch (single pass over the logits with a
+    rescaled running sum), three calls in a row on different data: the gather
+    buffer alternates with the device-side epoch and nothing leaks between calls."""
+    from nano_megatron_b200.ops import kernels
+
+    torch.manual_seed(11)
+    ex = kernels.CeExchange(n, torch.device(DEV))
+    for trial in range(3):
+        # growing maxima along the row exercise the rescaling of the running sum
+        logits = (_bf(n, v, scale=4.0).float() + torch.linspace(-6, 6, v, device=DEV) * (trial - 1)).to(torch.bfloat16)
+        target = torch.randint(0, v, (n,), device=DEV)
+        target[::5] = -100
+        lse, accum = kernels.ce_forward_fused(logits, target, 0, -100, ex)
+        ref_lse = torch.logsumexp(logits.float(), -1)
+        assert (lse - ref_lse).abs().max().item() < 2e-3
+        ref = F.cross_entropy(logits.float(), target, ignore_index=-100, reduction="sum")
+        assert abs(accum[0].item() - ref.item()) < 1e-3 * abs(ref.item()) + 1e-3
+        assert accum[1].item() == (target != -100).sum().item()
+
+
 def test_cross_entropy_two_simulated_vocab_shards():
     from nano_megatron_b200.ops import kernels
 

@@ -17,10 +17,27 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.abspath(__file__)
 
 
+class _CountingBackend:
+    """Delegates to the NCCL backend and counts the calls."""
+
+    def __init__(self):
+        from nano_megatron_b200.distributed.torch_backend import TorchDistBackend
+        self._inner = TorchDistBackend()
+        self.calls = 0
+
+    def __getattr__(self, name):
+        fn = getattr(self._inner, name)
+
+        def counted(*a, **kw):
+            self.calls += 1
+            return fn(*a, **kw)
+        return counted
+
+
 def _setup(symm=True, **cfg_kw):
     import nano_megatron_b200.parallel as P
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
-    ctx = P.initialize_parallel(P.ParallelConfig(**cfg_kw), dist_backend="nccl")
+    ctx = P.initialize_parallel(P.ParallelConfig(**cfg_kw), dist_backend="nccl", backend=_CountingBackend())
     made = {}
     if symm:
         from nano_megatron_b200.distributed.symm_mem import enable_symmetric_memory
@@ -102,14 +119,99 @@ def worker_ddp_symmetric():
     _finish(P)
 
 
+def worker_fused_gemm_ops():
+    """The three fused GEMM + collective launches against fp32 PyTorch, on any
+    world size: all-gather -> GEMM, GEMM -> reduce-scatter (+ bias + residual),
+    GEMM -> all-reduce (+ bias + residual).  Every launch is repeated 20 times
+    on the same inputs and must return the same bits (the flag protocol has no
+    data race), and a CUDA graph of back-to-back launches must agree as well."""
+    from nano_megatron_b200.ops import fused_tp
+    from nano_megatron_b200.ops.fused_tp import _place_shard, tp_fused_for
+    world = int(os.environ["WORLD_SIZE"])
+    P, ctx, _ = _setup(tensor_parallel_size=world, sequence_parallel=True)
+    st = tp_fused_for(ctx.tensor_parallel_group)
+    t, r = world, ctx.tensor_parallel_rank
+    b, s, h, k, n = 2, 256 * t, 320, 192, 416
+    rows = b * s
+    g = torch.Generator(device="cuda").manual_seed(100 + r)
+
+    def rnd(*shape):
+        return (torch.randn(*shape, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+
+    def gather(x):                      # [rows/t, c] shards -> [rows, c] in sequence order
+        parts = [torch.empty_like(x) for _ in range(t)]
+        dist.all_gather(parts, x.contiguous())
+        full = torch.stack([p.view(b, s // t, -1) for p in parts], dim=1)
+        return full.reshape(rows, -1)
+
+    def close(got, want, what):
+        rel = (got.float() - want).norm().item() / (want.norm().item() + 1e-9)
+        assert rel < 1e-2, (what, rel)
+        assert (got.float() - want).abs().max().item() < 0.06 * want.abs().max().item(), what
+
+    # ---- all-gather -> GEMM ----
+    shard, w, bias = rnd(b, s // t, h), rnd(n, h), rnd(n)
+    dist.broadcast(w, 0), dist.broadcast(bias, 0)
+    want = gather(shard.view(-1, h)).float() @ w.float().t() + bias.float()
+    first = None
+    for rep in range(20):
+        full = st.gather_buffer(rows, h, owner=("test", rep % 2))
+        _place_shard(full, shard, r, s, t)
+        got = st.allgather_gemm(full, w, s, bias=bias)
+        first = got.clone() if first is None else first
+        assert torch.equal(got, first), ("all-gather -> GEMM not repeatable", rep)
+        assert torch.equal(full, gather(shard.view(-1, h))), "gathered operand differs"
+    close(first, want, "all-gather -> GEMM")
+
+    # ---- GEMM -> reduce-scatter / all-reduce ----
+    a, w2, bias2 = rnd(rows, k), rnd(n, k), rnd(n)
+    dist.broadcast(bias2, 0)
+    res_full = rnd(rows, n)
+    dist.broadcast(res_full, 0)
+    partial = a.float() @ w2.float().t()
+    dist.all_reduce(partial)
+    want_full = partial + bias2.float() + res_full.float()
+    mine = torch.cat([want_full.view(b, s, n)[:, r * (s // t):(r + 1) * (s // t)]], 0).reshape(-1, n)
+    res_mine = res_full.view(b, s, n)[:, r * (s // t):(r + 1) * (s // t)].reshape(-1, n).contiguous()
+    first_rs = first_ar = None
+    for rep in range(20):
+        got = st.gemm_reduce_scatter(a, w2, s, bias=bias2, residual=res_mine)
+        first_rs = got.clone() if first_rs is None else first_rs
+        assert torch.equal(got, first_rs), ("GEMM -> reduce-scatter not repeatable", rep)
+        got = st.gemm_all_reduce(a, w2, bias=bias2, residual=res_full)
+        first_ar = got.clone() if first_ar is None else first_ar
+        assert torch.equal(got, first_ar), ("GEMM -> all-reduce not repeatable", rep)
+    close(first_rs, mine, "GEMM -> reduce-scatter")
+    close(first_ar, want_full, "GEMM -> all-reduce")
+    # every rank holds the same all-reduced bits
+    ref = first_ar.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(ref, first_ar), "all-reduce results differ between ranks"
+
+    # ---- a captured train of launches (odd length: consecutive replays end and start on the same buffers) ----
+    outs = []
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+        for i in range(3):
+            outs.append(st.gemm_all_reduce(a, w2, bias=bias2, residual=res_full))
+            outs.append(st.gemm_reduce_scatter(a, w2, s, bias=bias2, residual=res_mine))
+    for _ in range(6):
+        graph.replay()
+    torch.cuda.synchronize()
+    for i, o in enumerate(outs):
+        assert torch.equal(o, first_ar if i % 2 == 0 else first_rs), ("graph replay differs", i)
+    assert fused_tp.STATS["gemm_all_reduce"] >= 20
+    _finish(P)
+
+
 def _gpu_model_worker(knobs, seq=256, batch=2, tol=8e-2, **layout):
     from nano_megatron_b200.distributed import DistributedDataParallel
     from nano_megatron_b200.models import build_tp_gpt_from_reference
     from nano_megatron_b200.reference import ReferenceGPT, ReferenceGPTConfig, seed_all, shifted_cross_entropy
     P, ctx, _ = _setup(**layout)
     seed_all(0)
-    cfg = ReferenceGPTConfig(num_layers=2, hidden_size=256, num_heads=4, vocab_size=512, max_seq_len=seq,
-                             attn_backend="flash", **knobs)
+    cfg = ReferenceGPTConfig(**{**dict(num_layers=2, hidden_size=256, num_heads=4, vocab_size=512, max_seq_len=seq,
+                                       attn_backend="flash"), **knobs})
     ref = ReferenceGPT(cfg)
     with torch.no_grad():
         for p in ref.parameters():
@@ -120,11 +222,13 @@ def _gpu_model_worker(knobs, seq=256, batch=2, tol=8e-2, **layout):
     model = build_tp_gpt_from_reference(ref, ctx).to("cuda", dtype=torch.bfloat16)
     ddp = DistributedDataParallel(model, ctx)
     sl = slice(ctx.data_parallel_rank * batch, (ctx.data_parallel_rank + 1) * batch)
+    calls0 = ctx.backend.calls
     logits = ddp(ids[sl].cuda())
     loss = model.shifted_cross_entropy(logits, ids[sl].cuda())
     loss.backward()
     ddp.finish_grad_sync()
     torch.cuda.synchronize()
+    library_calls = ctx.backend.calls - calls0
     cpu_cfg = ReferenceGPTConfig(**{**cfg.__dict__, "attn_backend": "unfused"})
     ref.config = cpu_cfg
     for blk in ref.blocks:
@@ -143,76 +247,163 @@ def _gpu_model_worker(knobs, seq=256, batch=2, tol=8e-2, **layout):
         rel = (got - want).norm().item() / (want.norm().item() + 1e-6)
         assert rel < tol, (n, rel)
     _finish(P)
+    return library_calls
 
 
 GPT2 = dict(position_embedding_type="learned_absolute", gated_linear_unit=False, use_bias=True, use_fused_qkv=True)
 
 
-def worker_tp2_bf16():
-    _gpu_model_worker(GPT2, tensor_parallel_size=2)
-
-
-def worker_sp2_bf16():
+def worker_tp_bf16():
+    """Tensor parallelism without sequence parallelism over all ranks: every
+    collective of the step is a peer-memory kernel (GEMM -> all-reduce in the
+    row-parallel forward and the column-parallel dgrad, owner-writes embedding,
+    peer all-gather of the loss statistics) -- no library collective is called."""
     from nano_megatron_b200.ops import fused_tp
-    _gpu_model_worker(GPT2, tensor_parallel_size=2, sequence_parallel=True)
+    world = int(os.environ["WORLD_SIZE"])
+    calls = _gpu_model_worker(dict(GPT2, num_heads=8, hidden_size=512) if world == 8 else GPT2, seq=128 * world,
+                              tensor_parallel_size=world)
+    # 2 layers: (out, fc2) x 2 forward, (qkv, fc1) x 2 + lm_head dgrad backward
+    assert fused_tp.STATS["gemm_all_reduce"] >= 9, fused_tp.STATS
+    assert calls == 0, f"{calls} library collectives in a tensor-parallel step"
+
+
+def worker_sp_bf16():
+    from nano_megatron_b200.ops import fused_tp
+    world = int(os.environ["WORLD_SIZE"])
+    calls = _gpu_model_worker(dict(GPT2, num_heads=8, hidden_size=512) if world == 8 else GPT2, seq=128 * world,
+                              tensor_parallel_size=world, sequence_parallel=True)
     # 2 layers: (qkv, fc1) x 2 + lm_head gathers forward, (out, fc2) x 2 gathers backward, and the mirror image
     assert fused_tp.STATS["allgather_gemm"] >= 9 and fused_tp.STATS["gemm_reduce_scatter"] >= 9, fused_tp.STATS
+    assert calls == 0, f"{calls} library collectives in a sequence-parallel step"
 
 
-def worker_dp2_bf16():
+def worker_cp_bf16():
+    world = int(os.environ["WORLD_SIZE"])
+    _gpu_model_worker(dict(use_fused_qkv=True, use_bias=True), seq=128 * world, context_parallel_size=world)
+
+
+def worker_dp_bf16():
     _gpu_model_worker(dict(GPT2, tie_word_embeddings=True))
 
 
-def worker_cp2_bf16():
-    _gpu_model_worker(dict(use_fused_qkv=True, use_bias=True), context_parallel_size=2)
-
-
-def worker_pp2_bf16():
+def worker_pp_trainer():
+    """1F1B through ``PipelineTrainer``: PP2 (2 ranks), TP2 x PP2 (4), TP2 x PP2 x DP2 (8).
+    The step runs eagerly twice, is then captured per microbatch slot into CUDA
+    graphs and replayed; loss and EVERY gradient must agree between the eager
+    and the graphed step and with the fp32 CPU oracle on the global batch."""
+    from nano_megatron_b200.engine import PipelineTrainer
     from nano_megatron_b200.models import build_pipeline_stage_from_reference
     from nano_megatron_b200.reference import ReferenceGPT, ReferenceGPTConfig, seed_all, shifted_cross_entropy
-    from nano_megatron_b200.schedules import forward_backward_1f1b
-    P, ctx, _ = _setup(symm=False, pipeline_parallel_size=2)
+    from tests.test_distributed_gloo import _expected_shard
+    world = int(os.environ["WORLD_SIZE"])
+    tp = 1 if world == 2 else 2
+    P, ctx, _ = _setup(tensor_parallel_size=tp, pipeline_parallel_size=2)
     seed_all(0)
     cfg = ReferenceGPTConfig(num_layers=4, hidden_size=256, num_heads=4, vocab_size=512, max_seq_len=256,
                              attn_backend="flash", **GPT2)
     ref = ReferenceGPT(cfg)
-    ids = torch.randint(0, cfg.vocab_size, (4, 256))
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() > 1:
+                p.mul_(0.5)
+    dp, m, per_rank = ctx.data_parallel_size, 4, 8
+    ids = torch.randint(0, cfg.vocab_size, (per_rank * dp, 256))
+    mine = ids[ctx.data_parallel_rank * per_rank:(ctx.data_parallel_rank + 1) * per_rank].cuda()
     stage = build_pipeline_stage_from_reference(ref, ctx).to("cuda", dtype=torch.bfloat16)
-    loss = forward_backward_1f1b(stage=stage, ctx=ctx, input_ids=ids.cuda(), labels=ids.cuda(), num_microbatches=2)
-    torch.cuda.synchronize()
+    trainer = PipelineTrainer(stage, ctx, num_microbatches=m, lr=0.0, weight_decay=0.0)
+    last = P.is_pipeline_last_stage(ctx)
+    runs = []
+    for step in range(4):
+        calls0 = ctx.backend.calls
+        loss = trainer.forward_backward(mine)
+        torch.cuda.synchronize()
+        runs.append((trainer.graphed, None if loss is None else loss.item(),
+                     {n: p.grad.float().clone() for n, p in stage.named_parameters()}, ctx.backend.calls - calls0))
+    assert trainer.graphed, trainer.graph_error
+    assert not runs[0][0] and runs[-1][0]
+    eager, graphed = runs[0], runs[-1]
+    if last:
+        assert abs(eager[1] - graphed[1]) <= 1e-3 * abs(eager[1]), (eager[1], graphed[1])
+    for n in eager[2]:
+        a, b = eager[2][n], graphed[2][n]
+        assert (a - b).norm().item() <= 2e-3 * (a.norm().item() + 1e-6), ("eager vs graphed", n)
+    # the graphed step calls the library only for the pipeline's point-to-point transfers
+    assert graphed[3] <= 2 * m, graphed[3]
     cpu_cfg = ReferenceGPTConfig(**{**cfg.__dict__, "attn_backend": "unfused"})
     ref.config = cpu_cfg
     for blk in ref.blocks:
         blk.attn.config = cpu_cfg
     ref_loss = shifted_cross_entropy(ref(ids), ids)
-    if P.is_pipeline_last_stage(ctx):
-        assert abs(loss.item() - ref_loss.item()) < 3e-2 * abs(ref_loss.item())
+    ref_loss.backward()
+    if last:
+        avg = torch.tensor([graphed[1]], device="cuda")
+        dist.all_reduce(avg, group=ctx.data_parallel_group)
+        assert abs(avg.item() / dp - ref_loss.item()) < 3e-2 * abs(ref_loss.item()), (avg.item() / dp, ref_loss.item())
+    offset = ctx.pipeline_parallel_rank * (cfg.num_layers // 2)
+
+    def rename(n):
+        if n.startswith("blocks."):
+            _, idx, rest = n.split(".", 2)
+            return f"blocks.{int(idx) + offset}.{rest}"
+        return n
+
+    ref_grads = {n: p.grad for n, p in ref.named_parameters()}
+    for n, got in graphed[2].items():
+        want = _expected_shard(rename(n), ref_grads[rename(n)], ctx, cfg)
+        rel = (got.cpu() - want).norm().item() / (want.norm().item() + 1e-6)
+        assert rel < 8e-2, (n, rel)
     _finish(P)
 
 
-def worker_peer_leaves_between_steps():
-    """A rank stops between steps (nothing in flight); the survivor's next
-    collective ends with an error from the process-group timeout, not a hang."""
-    import datetime
-    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
-    dist.init_process_group("nccl", timeout=datetime.timedelta(seconds=10))
-    t = torch.ones(4, device="cuda")
-    dist.all_reduce(t)
-    torch.cuda.synchronize()
-    if dist.get_rank() == 1:
-        os._exit(0)                      # leaves between steps
-    try:
-        dist.all_reduce(t)
-        torch.cuda.synchronize()
-        survived = False
-    except Exception:
-        survived = True
-    print("SURVIVOR_SAW_ERROR" if survived else "SURVIVOR_SAW_NOTHING", flush=True)
-    os._exit(0)
+def worker_trainer_graph_tp():
+    """``Trainer`` on tensor parallelism without sequence parallelism: the whole
+    step (no library collective left in it) is captured into one CUDA graph;
+    the loss trajectory of the graphed steps continues the eager one and matches
+    a second, never-graphed trainer; the optimizer state survives a save /
+    load round trip under the captured graph."""
+    from nano_megatron_b200.engine import Trainer
+    from nano_megatron_b200.models import build_tp_gpt_from_reference
+    from nano_megatron_b200.reference import ReferenceGPT, ReferenceGPTConfig, seed_all
+    world = int(os.environ["WORLD_SIZE"])
+    P, ctx, _ = _setup(tensor_parallel_size=world)
+    cfg = ReferenceGPTConfig(num_layers=2, hidden_size=256, num_heads=4, vocab_size=512, max_seq_len=256,
+                             attn_backend="flash", **GPT2)
+    ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(3)).cuda()
+
+    def make(graph):
+        seed_all(0)
+        model = build_tp_gpt_from_reference(ReferenceGPT(cfg), ctx).to("cuda", dtype=torch.bfloat16)
+        return Trainer(model, ctx, lr=1e-3, use_cuda_graph=graph)
+
+    a, b = make(True), make(False)
+    la = [a.step(ids).item() for _ in range(8)]
+    lb = [b.step(ids).item() for _ in range(8)]
+    assert a.graphed, a.graph_error
+    assert not b.graphed
+    for x, y in zip(la, lb):
+        assert abs(x - y) <= 2e-2 * abs(y), (la, lb)
+    assert la[-1] < la[0]
+    # state round trip under the graph: the replayed graph must see the loaded moments
+    state = a.optimizer.state_dict()
+    params = {n: p.detach().clone() for n, p in a.model.named_parameters()}
+    after = a.step(ids).item()
+    a.optimizer.load_state_dict(state)
+    with torch.no_grad():
+        for n, p in a.model.named_parameters():
+            p.copy_(params[n])
+    again = a.step(ids).item()
+    assert abs(after - again) <= 1e-3 * abs(after), (after, again)
+    _finish(P)
 
 
-CASES = [("worker_symm_allreduce", 2), ("worker_ddp_symmetric", 2), ("worker_tp2_bf16", 2), ("worker_sp2_bf16", 2),
-         ("worker_dp2_bf16", 2), ("worker_cp2_bf16", 2), ("worker_pp2_bf16", 2)]
+CASES = [("worker_symm_allreduce", 2), ("worker_ddp_symmetric", 2), ("worker_fused_gemm_ops", 2),
+         ("worker_tp_bf16", 2), ("worker_sp_bf16", 2), ("worker_dp_bf16", 2), ("worker_cp_bf16", 2),
+         ("worker_pp_trainer", 2), ("worker_trainer_graph_tp", 2),
+         # the layouts the benchmark runs at 4 and 8 GPUs
+         ("worker_fused_gemm_ops", 4), ("worker_tp_bf16", 4), ("worker_sp_bf16", 4), ("worker_cp_bf16", 4),
+         ("worker_pp_trainer", 4),
+         ("worker_fused_gemm_ops", 8), ("worker_tp_bf16", 8), ("worker_sp_bf16", 8), ("worker_cp_bf16", 8),
+         ("worker_dp_bf16", 8), ("worker_ddp_symmetric", 8), ("worker_pp_trainer", 8)]
 
 
 @pytest.mark.parametrize("worker,world", CASES, ids=[f"{w}-{n}" for w, n in CASES])

@@ -24,6 +24,7 @@ pytestmark = pytest.mark.gpu
 def _call(lib, dy, out, accumulate=0):
     rows, cols = dy.shape
     lib.nmb_col_sum_noalloc.restype = ctypes.c_int
+    lib.nmb_col_sum_noalloc_strerror.restype = ctypes.c_char_p
     return lib.nmb_col_sum_noalloc(
         ctypes.c_void_p(dy.data_ptr()), ctypes.c_int(dy.stride(0)), ctypes.c_void_p(out.data_ptr()),
         ctypes.c_int(rows), ctypes.c_int(cols), ctypes.c_int(accumulate),
@@ -73,3 +74,27 @@ def test_no_alloc_col_sum_rejects_oversize_and_odd_shapes():
     odd = torch.zeros(4, 6, dtype=torch.bfloat16, device="cuda")[:, :5]
     assert _call(lib, odd, out) == 3
     torch.cuda.synchronize()
+
+
+def test_no_alloc_col_sum_rejects_misaligned_view_and_zeroes_on_no_rows():
+    """A bf16 view that starts at an odd element (even pitch, even width) would be
+    read with misaligned 4-byte loads: it must be refused before any launch."""
+    from nano_megatron_b200.ops import native
+
+    lib = native.lib()
+    wide = torch.randn(64, 256, device="cuda").to(torch.bfloat16)
+    view = wide[:, 1:129]
+    assert view.data_ptr() % 4 == 2 and view.stride(0) % 2 == 0 and view.shape[1] % 2 == 0
+    out = torch.full((128,), 3.0, dtype=torch.bfloat16, device="cuda")
+    rc = _call(lib, view, out)
+    assert rc == 3 and b"aligned" in lib.nmb_col_sum_noalloc_strerror(rc)
+    torch.cuda.synchronize()
+    assert torch.all(out == 3.0)            # nothing was launched
+    # no rows: the sum over nothing is zero (kept when accumulating)
+    empty = wide[:0, :128]
+    assert _call(lib, empty, out, accumulate=1) == 0
+    torch.cuda.synchronize()
+    assert torch.all(out == 3.0)
+    assert _call(lib, empty, out) == 0
+    torch.cuda.synchronize()
+    assert torch.all(out == 0.0)
