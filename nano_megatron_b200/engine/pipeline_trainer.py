@@ -109,6 +109,16 @@ class PipelineTrainer:
                 return False
         return True
 
+    def _parameters_write_directly(self) -> bool:
+        """Every parameter's gradient is accumulated into its bucket buffer by the
+        backward kernels themselves (``main_grad``).  Parameters whose gradient
+        comes back through autograd (replicated parameters under sequence
+        parallelism, whose hook reduces them over the TP group) need the eager
+        schedule: the graphed backward of a later stage asks autograd only for the
+        gradient of the stage input."""
+        return all(getattr(p, "main_grad", None) is not None and not getattr(p, "_nmb_sp_replicated", False)
+                   for p in self.stage.parameters() if p.requires_grad)
+
     @property
     def graphed(self) -> bool:
         return bool(self._slots)
@@ -132,6 +142,10 @@ class PipelineTrainer:
                              f"got {tuple(input_ids.shape)}")
         self.ddp.zero_grad()
         if self._want_graph and not self._slots and self._eager_steps >= self._graph_warmup:
+            if not self._parameters_write_directly():
+                self._want_graph = False
+                self.graph_error = "not captured: some parameter gradients are delivered through autograd"
+        if self._want_graph and not self._slots and self._eager_steps >= self._graph_warmup:
             self._capture(input_ids.shape[0] // self.m, input_ids.shape[1])
         if self._slots and self._shape == (input_ids.shape[0] // self.m, input_ids.shape[1]):
             return self._run_graphed(input_ids, labels)
@@ -141,10 +155,11 @@ class PipelineTrainer:
 
     # ---------------------------------------------------------------- capture --
     def _capture(self, mb: int, seq: int) -> None:
-        """Capture forward and backward of every slot.  All ranks of the stage's
-        tensor-parallel group capture the same kernels in the same order (the
-        peer-memory collectives meet during capture-time warm-up runs only)."""
+        """Capture forward and backward of every slot.  Nothing executes during a
+        capture, so no rank waits for another here; all ranks of the stage's
+        tensor-parallel group record the same kernels in the same order."""
         self._want_graph = False
+        where = "set-up"
         stage = self.stage
         n_slots = min(self.n_warm + 1, self.m)
         act_shape = stage.activation_shape(mb, seq)
@@ -167,6 +182,7 @@ class PipelineTrainer:
                 else:
                     slot.grad_out = torch.zeros(act_shape, dtype=self.dtype, device=self.device)
                 slot.fwd, slot.bwd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+                where = f"forward of slot {s}"
                 with torch.cuda.graph(slot.fwd, capture_error_mode="thread_local"):
                     out = stage(slot.x, positions=slot.positions)
                     if self.last:
@@ -174,19 +190,32 @@ class PipelineTrainer:
                         self._loss_acc.add_(out.detach().float())
                     slot.out = out
                 pool = slot.fwd.pool()
+                where = f"backward of slot {s}"
                 with torch.cuda.graph(slot.bwd, pool=pool, capture_error_mode="thread_local"):
                     with self.ddp.no_sync():
-                        if self.last:
-                            slot.out.backward(retain_graph=True)
+                        if self.first:
+                            # no differentiable input: parameters only (their gradients are
+                            # written into the bucket buffers by the backward kernels)
+                            if self.last:
+                                slot.out.backward(retain_graph=True)
+                            else:
+                                torch.autograd.backward(slot.out, grad_tensors=slot.grad_out, retain_graph=True)
                         else:
-                            torch.autograd.backward(slot.out, grad_tensors=slot.grad_out, retain_graph=True)
-                    if not self.first:
-                        slot.grad_in = slot.x.grad
+                            # The input gradient is asked for explicitly, so that no
+                            # gradient-accumulation node of a leaf runs inside the capture;
+                            # the parameter gradients are side effects of the same backward
+                            # functions (checked in _parameters_write_directly).
+                            (slot.grad_in,) = torch.autograd.grad(
+                                [slot.out], [slot.x], grad_outputs=None if self.last else [slot.grad_out],
+                                retain_graph=True)
                 slots.append(slot)
             self.kernels_in_graph = (native.launches - before) * self.m // n_slots
             self._slots, self._shape = slots, (mb, seq)
         except Exception as exc:  # pragma: no cover - depends on the device
-            self.graph_error = f"{type(exc).__name__}: {exc}"
+            import traceback
+            frames = traceback.extract_tb(exc.__traceback__)
+            trail = " <- ".join(f"{f.name}:{f.lineno}" for f in frames[-4:])
+            self.graph_error = f"capture of the {where} failed: {type(exc).__name__}: {str(exc)[:300]} [{trail}]"
             self._slots = []
             torch.cuda.synchronize(self.device)
         finally:

@@ -25,6 +25,7 @@ sequence parallelism) their forward and backward in terms of these launches.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Any, Optional
 
 import torch
@@ -36,7 +37,8 @@ from .gemm import EPI_DGELU, EPI_GELU, EPI_PLAIN, gemm_bf16
 from ..utils.tracing import nvtx_range
 
 _MAX = 8
-COPY_CTAS = 16
+#: CTAs of an all-gather -> GEMM launch that only copy (NMB_AG_COPY_CTAS overrides)
+COPY_CTAS = int(os.environ.get("NMB_AG_COPY_CTAS", "16"))
 #: switched on by ``enable_symmetric_memory``
 ENABLED = False
 #: launches of the fused kernels by this process (tests assert on it)

@@ -99,9 +99,12 @@ def main(argv=None) -> int:
     b, s, h, f, t = args.batch, args.seq, args.hidden, args.ffn, world
     rows = b * s
 
-    def report(name: str, us_graph: float, us_fused: float, us_plain: float, flops: float, link_bytes: float) -> None:
+    def report(name: str, us_graph: float, us_fused: float, us_plain: float, flops: float, link_bytes: float,
+               us_gemm: float = 0.0) -> None:
         if rank != 0:
             return
+        if us_gemm:
+            name = f"{name} (GEMM alone {us_gemm:.1f} us)"
         t_compute = flops / (peaks["bf16_tflops"] * 1e12) * 1e6
         t_link = link_bytes / (NVLINK_GBS * 1e9) * 1e6
         target = max(t_compute, t_link)
@@ -130,7 +133,7 @@ def main(argv=None) -> int:
 
         report(f"all-gather -> GEMM {label} [{rows} x {n_out} x {h}]", _graphed(fused, sets, length),
                _train(fused, sets, length), _train(plain, sets, length), 2.0 * rows * n_out * h,
-               rows * h * 2.0 * (t - 1) / t)
+               rows * h * 2.0 * (t - 1) / t, _graphed(lambda i: gemm_bf16(gathered[i], w), sets, length))
 
     # ---- GEMM -> reduce-scatter (row-parallel linear under SP), GEMM -> all-reduce (without SP) ----
     for label, k_in in (("proj", h // t), ("fc2", f // t)):
@@ -156,7 +159,7 @@ def main(argv=None) -> int:
 
         report(f"GEMM -> reduce-scatter {label} [{rows} x {h} x {k_in}]", _graphed(fused_rs, sets, length),
                _train(fused_rs, sets, length), _train(plain_rs, sets, length), 2.0 * rows * h * k_in,
-               rows * h * 2.0 * (t - 1) / t)
+               rows * h * 2.0 * (t - 1) / t, _graphed(lambda i: gemm_bf16(a[i], w), sets, length))
         if st.all_reduce_supported(rows, h):
             report(f"GEMM -> all-reduce {label} [{rows} x {h} x {k_in}]", _graphed(fused_ar, sets, length),
                    _train(fused_ar, sets, length), _train(plain_ar, sets, length), 2.0 * rows * h * k_in,

@@ -325,8 +325,10 @@ def worker_pp_trainer():
     if last:
         assert abs(eager[1] - graphed[1]) <= 1e-3 * abs(eager[1]), (eager[1], graphed[1])
     for n in eager[2]:
-        a, b = eager[2][n], graphed[2][n]
-        assert (a - b).norm().item() <= 2e-3 * (a.norm().item() + 1e-6), ("eager vs graphed", n)
+        a, b, a2 = eager[2][n], graphed[2][n], runs[1][2][n]
+        # two eager runs differ where bf16 atomics accumulate (embedding rows hit several times)
+        noise = (a - a2).norm().item()
+        assert (a - b).norm().item() <= max(2e-3 * (a.norm().item() + 1e-6), 4 * noise), ("eager vs graphed", n)
     # the graphed step calls the library only for the pipeline's point-to-point transfers
     assert graphed[3] <= 2 * m, graphed[3]
     cpu_cfg = ReferenceGPTConfig(**{**cfg.__dict__, "attn_backend": "unfused"})
