@@ -868,15 +868,66 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const 
   }
 }
 
-// dq (bf16, strided) <- dq_acc (fp32, [B, H, S, d] with the 16-byte chunks of a
-// row XOR-swizzled by (s % 128) & 7 inside each group of eight); 8 elements per thread.
+// Inverse rotary rotation of 8 consecutive elements (4 interleaved pairs starting
+// at pair `pair0` of the head) of the row at position `pos`: the gradient with
+// respect to the un-rotated projection output, R(-angle) applied to the gradient
+// of the rotated one.
+__device__ __forceinline__ void unrope8(float (&x)[8], const float2* table, long long pos, int half, int pair0) {
+  const float4* tp = reinterpret_cast<const float4*>(table + pos * half + pair0);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const float4 cs = __ldg(tp + q);
+    const float a0 = x[4 * q], a1 = x[4 * q + 1], b0 = x[4 * q + 2], b1 = x[4 * q + 3];
+    x[4 * q] = a0 * cs.x + a1 * cs.y;
+    x[4 * q + 1] = -a0 * cs.y + a1 * cs.x;
+    x[4 * q + 2] = b0 * cs.z + b1 * cs.w;
+    x[4 * q + 3] = -b0 * cs.w + b1 * cs.z;
+  }
+}
+
+// Last kernel of the backward pass.
+//   * dq (bf16, strided) <- dq_acc (fp32, [B, H, S, d] with the 16-byte chunks of
+//     a row XOR-swizzled by (s % 128) & 7 inside each group of eight); 8 elements
+//     per thread;
+//   * with a rotary table (q and k were rotated by the epilogue of the QKV
+//     projection): dq is un-rotated on the way out and dk (already written by
+//     the main kernel, bf16) is un-rotated in place by the threads past the dq
+//     range -- so the projection's backward sees plain gradients and no separate
+//     rotation kernel runs (the reference differentiates through ~10 elementwise
+//     kernels per tensor, nano_megatron/reference/layers.py:67-81).
 __global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dq,
                                      long long dq_sb, long long dq_ss, long long dq_sh, int B, int H,
-                                     int S, int d) {
+                                     int S, int d, const float2* __restrict__ rope_table,
+                                     const long long* __restrict__ rope_pos, __nv_bfloat16* __restrict__ dk,
+                                     long long dk_sb, long long dk_ss, long long dk_sh, int Hkv) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long total = static_cast<long long>(B) * S * H * d / 8;
-  if (idx >= total) return;
   const int per_row = d / 8;
+  if (idx >= total) {
+    if (rope_table == nullptr || dk == nullptr) return;
+    const long long j = idx - total;
+    if (j >= static_cast<long long>(B) * S * Hkv * per_row) return;
+    const int c8 = static_cast<int>(j % per_row);
+    const long long row = j / per_row;              // (b * S + s) * Hkv + h
+    const int h = row % Hkv;
+    const long long bs = row / Hkv;
+    const int s = bs % S;
+    const int b = bs / S;
+    uint4* p = reinterpret_cast<uint4*>(dk + b * dk_sb + s * dk_ss + h * dk_sh + c8 * 8);
+    const uint4 u = *p;
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    float x[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack_bf16x2(w[k]);
+      x[2 * k] = f.x;
+      x[2 * k + 1] = f.y;
+    }
+    unrope8(x, rope_table, rope_pos[static_cast<long long>(b) * S + s], d / 2, c8 * 4);
+    *p = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]),
+                    pack_bf16x2(x[6], x[7]));
+    return;
+  }
   const int c8 = static_cast<int>(idx % per_row);   // which 8 columns of the row
   const long long row = idx / per_row;              // (b * H + h) * S + s
   const int s = row % S;
@@ -888,11 +939,13 @@ __global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bflo
   const int c0 = 2 * c8, c1 = 2 * c8 + 1;           // the two 16-byte chunks
   const float4 v0 = *reinterpret_cast<const float4*>(src + ((c0 & ~7) | ((c0 ^ r) & 7)) * 4);
   const float4 v1 = *reinterpret_cast<const float4*>(src + ((c1 & ~7) | ((c1 ^ r) & 7)) * 4);
+  float x[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  if (rope_table != nullptr) unrope8(x, rope_table, rope_pos[static_cast<long long>(b) * S + s], d / 2, c8 * 4);
   uint4 out;
-  out.x = pack_bf16x2(v0.x, v0.y);
-  out.y = pack_bf16x2(v0.z, v0.w);
-  out.z = pack_bf16x2(v1.x, v1.y);
-  out.w = pack_bf16x2(v1.z, v1.w);
+  out.x = pack_bf16x2(x[0], x[1]);
+  out.y = pack_bf16x2(x[2], x[3]);
+  out.z = pack_bf16x2(x[4], x[5]);
+  out.w = pack_bf16x2(x[6], x[7]);
   *reinterpret_cast<uint4*>(dq + b * dq_sb + s * dq_ss + h * dq_sh + c8 * 8) = out;
 }
 
@@ -984,8 +1037,8 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
                             int n_chunks, int chunk_len, const NmbTensor4* o, const NmbTensor4* dout,
                             const float* lse, float* delta, float* dq_acc, const NmbTensor4* dq,
                             const NmbTensor4* dk_chunks, const NmbTensor4* dv_chunks, int B, int Hq, int Hkv,
-                            int Sq, int d, int q_pos0, int n_visible_kv_tiles, float scale, int* status,
-                            void* stream) {
+                            int Sq, int d, int q_pos0, int n_visible_kv_tiles, float scale,
+                            const void* rope_table, const long long* rope_pos, int* status, void* stream) {
   if (n_chunks < 1 || n_chunks > kMaxChunks) return kBadArgument;
   if (d != 64 && d != 96 && d != 128) return kBadArgument;
   if (n_chunks > 1 && (chunk_len % 128) != 0) return kBadArgument;
@@ -1032,10 +1085,16 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   e = cudaGetLastError();
   if (e != cudaSuccess) return 400 + e;
   {
-    const long long octets = static_cast<long long>(B) * Sq * Hq * d / 8;
+    // un-rotating dk in place needs the whole key sequence in one local chunk of the query's length
+    const bool unrope_k = rope_table != nullptr && n_chunks == 1 && chunk_len == Sq;
+    if (rope_table != nullptr && !unrope_k) return kBadArgument;
+    long long octets = static_cast<long long>(B) * Sq * Hq * d / 8;
+    if (unrope_k) octets += static_cast<long long>(B) * Sq * Hkv * d / 8;
     const int threads = 256;
     attn_dq_store_kernel<<<static_cast<unsigned>((octets + threads - 1) / threads), threads, 0, s>>>(
-        dq_acc, static_cast<__nv_bfloat16*>(dq->ptr), dq->stride_b, dq->stride_s, dq->stride_h, B, Hq, Sq, d);
+        dq_acc, static_cast<__nv_bfloat16*>(dq->ptr), dq->stride_b, dq->stride_s, dq->stride_h, B, Hq, Sq, d,
+        static_cast<const float2*>(rope_table), rope_pos, unrope_k ? static_cast<__nv_bfloat16*>(dk_chunks[0].ptr) : nullptr,
+        dk_chunks[0].stride_b, dk_chunks[0].stride_s, dk_chunks[0].stride_h, Hkv);
   }
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + e;

@@ -36,6 +36,9 @@ enum EpilogueMode : int {
   kEpiPlain = 0,   // C = acc (+bias) (+residual) (+C_old)
   kEpiGelu = 1,    // aux_out = acc+bias ; C = gelu(acc+bias)
   kEpiDGelu = 2,   // C = acc * gelu'(aux_in)
+  kEpiRope = 3,    // C = rope(acc + bias) on the first rope_cols columns (interleaved pairs), rest unchanged
+  kEpiSwiGLU = 4,  // B rows are [gate; up] (F each): aux_out = [gate | up] + bias ; C[:, :F] = silu(gate) * up
+  kEpiDSwiGLU = 5, // acc = d(act) [M, F]: C[:, :F] = d gate, C[:, F:] = d up, from aux_in = [gate | up]
 };
 
 struct GemmEpilogue {
@@ -51,6 +54,24 @@ struct GemmEpilogue {
   int accumulate;           // add the previous contents of C
   int out_f32;              // C is fp32
   float alpha;              // scale applied to the accumulator first
+  // kEpiRope: rotary position embedding fused into the projection that produces q and k
+  // (the reference rotates after the projection with ~10 elementwise kernels per tensor,
+  // nano_megatron/reference/layers.py:67-81).  Pair i of a head is rotated by the angle
+  // whose (cos, sin) is rope_table[rope_pos[row]][i].
+  const float2* rope_table;     // [positions][rope_half]
+  const long long* rope_pos;    // [M]
+  int rope_cols;                // leading columns that hold q and k heads
+  int rope_half;                // head_dim / 2
+  int swiglu_f;                 // kEpiSwiGLU / kEpiDSwiGLU: F
+};
+
+// Extra epilogue arguments of the C entry points (all optional).
+struct NmbEpilogueExtra {
+  const void* rope_table;
+  const long long* rope_pos;
+  int rope_cols;
+  int rope_half;
+  int swiglu_f;
 };
 
 // Collective fused into the GEMM (both optional, normally one at a time).
@@ -286,7 +307,9 @@ __device__ __forceinline__ void fused_leave(const FusedComm& fc, uint32_t epoch)
 // Epilogue of one 128-row accumulator tile for one warp: drains its half of
 // the BN columns of TMEM lane quadrant `t_row` (32 columns at a time), applies
 // alpha / bias / GELU / dGELU / residual / accumulate and stores row `row`.
-template <int BN>
+// FULL adds the rotary and SwiGLU-backward epilogues (only compiled into the
+// kernel instantiation that also carries the fused collectives).
+template <int BN, bool FULL>
 __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const FusedComm& fc, uint32_t t_row, int row,
                                                  bool row_ok, int n0, int half, int N) {
 #pragma unroll 1
@@ -315,6 +338,45 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
             v[q * 8 + t * 2 + 1] += f.y;
           }
         }
+      }
+      if (FULL && ep.mode == kEpiRope && col0 < ep.rope_cols) {
+        // 16 interleaved pairs of one head; their angles are consecutive table entries
+        const int pair0 = (col0 % (2 * ep.rope_half)) >> 1;
+        const float4* tp = reinterpret_cast<const float4*>(ep.rope_table + ep.rope_pos[row] * ep.rope_half + pair0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 cs = __ldg(tp + q);
+          const float a0 = v[4 * q], a1 = v[4 * q + 1], b0 = v[4 * q + 2], b1 = v[4 * q + 3];
+          v[4 * q] = a0 * cs.x - a1 * cs.y;
+          v[4 * q + 1] = a0 * cs.y + a1 * cs.x;
+          v[4 * q + 2] = b0 * cs.z - b1 * cs.w;
+          v[4 * q + 3] = b0 * cs.w + b1 * cs.z;
+        }
+      }
+      if (FULL && ep.mode == kEpiDSwiGLU) {
+        // v = d(act); gate / up pre-activations from the forward pass
+        const __nv_bfloat16* pre = ep.aux_in + static_cast<size_t>(row) * ep.ld_aux + col0;
+        __nv_bfloat16* c_row = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc + col0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 gu = reinterpret_cast<const uint4*>(pre)[q];
+          const uint4 uu = reinterpret_cast<const uint4*>(pre + ep.swiglu_f)[q];
+          const uint32_t gw[4] = {gu.x, gu.y, gu.z, gu.w};
+          const uint32_t uw[4] = {uu.x, uu.y, uu.z, uu.w};
+          uint32_t og[4], ou[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 g = unpack_bf16x2(gw[t]);
+            const float2 u = unpack_bf16x2(uw[t]);
+            const float d0 = v[q * 8 + t * 2], d1 = v[q * 8 + t * 2 + 1];
+            const float s0 = 1.f / (1.f + __expf(-g.x)), s1 = 1.f / (1.f + __expf(-g.y));
+            og[t] = pack_bf16x2(d0 * u.x * s0 * (1.f + g.x * (1.f - s0)), d1 * u.y * s1 * (1.f + g.y * (1.f - s1)));
+            ou[t] = pack_bf16x2(d0 * g.x * s0, d1 * g.y * s1);
+          }
+          reinterpret_cast<uint4*>(c_row)[q] = make_uint4(og[0], og[1], og[2], og[3]);
+          reinterpret_cast<uint4*>(c_row + ep.swiglu_f)[q] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+        }
+        continue;
       }
       if (ep.mode == kEpiGelu) {
         uint4* ap = reinterpret_cast<uint4*>(ep.aux_out + static_cast<size_t>(row) * ep.ld_aux + col0);
@@ -431,6 +493,64 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
   }
 }
 
+// SwiGLU forward epilogue (BN = 256): accumulator columns 0..127 are the gate,
+// 128..255 the up projection of output features [n0/2, n0/2 + 128).  Each warp
+// takes 64 features: stores gate + bias and up + bias into aux_out = [gate | up]
+// (what the backward pass needs) and silu(gate) * up into C.  The activation is
+// computed from the bf16-rounded pre-activations, as the backward will see them.
+__device__ __forceinline__ void epilogue_swiglu(const GemmEpilogue& ep, uint32_t t_row, int row, bool row_ok, int n0,
+                                                int half) {
+  const int F = ep.swiglu_f;
+#pragma unroll 1
+  for (int c = 2 * half; c < 2 * half + 2; ++c) {
+    const int col0 = (n0 >> 1) + c * 32;
+    if (col0 >= F) break;  // uniform across the warp (F is a multiple of 32)
+    uint32_t rg[32], ru[32];
+    tmem_ld_32x32(t_row + c * 32, rg);
+    tmem_ld_32x32(t_row + 128 + c * 32, ru);
+    tmem_ld_wait();
+    if (!row_ok) continue;
+    __nv_bfloat16* pre = ep.aux_out + static_cast<size_t>(row) * ep.ld_aux + col0;
+    __nv_bfloat16* act = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc + col0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float g[8], u[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        g[t] = __uint_as_float(rg[q * 8 + t]) * ep.alpha;
+        u[t] = __uint_as_float(ru[q * 8 + t]) * ep.alpha;
+      }
+      if (ep.bias != nullptr) {
+        const uint4 bg = __ldg(reinterpret_cast<const uint4*>(ep.bias + col0) + q);
+        const uint4 bu = __ldg(reinterpret_cast<const uint4*>(ep.bias + F + col0) + q);
+        const uint32_t wg[4] = {bg.x, bg.y, bg.z, bg.w};
+        const uint32_t wu[4] = {bu.x, bu.y, bu.z, bu.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 a = unpack_bf16x2(wg[t]);
+          const float2 b = unpack_bf16x2(wu[t]);
+          g[2 * t] += a.x;
+          g[2 * t + 1] += a.y;
+          u[2 * t] += b.x;
+          u[2 * t + 1] += b.y;
+        }
+      }
+      uint32_t pg[4], pu[4], pa[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        pg[t] = pack_bf16x2(g[2 * t], g[2 * t + 1]);
+        pu[t] = pack_bf16x2(u[2 * t], u[2 * t + 1]);
+        const float2 gr = unpack_bf16x2(pg[t]);
+        const float2 ur = unpack_bf16x2(pu[t]);
+        pa[t] = pack_bf16x2(gr.x / (1.f + __expf(-gr.x)) * ur.x, gr.y / (1.f + __expf(-gr.y)) * ur.y);
+      }
+      reinterpret_cast<uint4*>(pre)[q] = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+      reinterpret_cast<uint4*>(pre + F)[q] = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+      reinterpret_cast<uint4*>(act)[q] = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+    }
+  }
+}
+
 // Epilogue of a tile whose rows take part in a fused reduce-scatter /
 // all-reduce (N is a multiple of 32 there, rows are whole 128-row blocks).
 //   own == false: the tile belongs to another rank: store the bf16 partial into
@@ -530,9 +650,10 @@ __device__ __forceinline__ void epilogue_columns_reduce(const GemmEpilogue& ep, 
   }
 }
 
-// FUSED selects the instantiation that carries the collective code paths (copy
-// CTAs, reduce epilogue); the plain one stays at the register count that lets a
-// block of the overlapped gradient all-reduce share its SM.
+// FUSED selects the instantiation that carries the optional code paths (copy
+// CTAs and reduce epilogue of the fused collectives, rotary / SwiGLU
+// epilogues); the plain one stays at the register count that lets a block of
+// the overlapped gradient all-reduce share its SM.
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -667,7 +788,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               tma_load_2d(sa + c * 8192, &tma_a, &full_bar[stage], m0 + c * 64, kb * kBK);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * kBK, n0);
+            if (FUSED && BN == 256 && ep.mode == kEpiSwiGLU) {
+              // 128 gate rows and the 128 up rows of the same output features
+              tma_load_2d(sb, &tma_b, &full_bar[stage], kb * kBK, n0 >> 1);
+              tma_load_2d(sb + 16384, &tma_b, &full_bar[stage], kb * kBK, ep.swiglu_f + (n0 >> 1));
+            } else {
+              tma_load_2d(sb, &tma_b, &full_bar[stage], kb * kBK, n0);
+            }
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
@@ -754,7 +881,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const bool row_ok = row < M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
       if (!reducing) {
-        epilogue_columns<BN>(ep, fc, t_row, row, row_ok, n0, half, N);
+        if (FUSED && BN == 256 && ep.mode == kEpiSwiGLU)
+          epilogue_swiglu(ep, t_row, row, row_ok, n0, half);
+        else
+          epilogue_columns<BN, FUSED>(ep, fc, t_row, row, row_ok, n0, half, N);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -1056,7 +1186,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
-      epilogue_columns<BN>(ep, fc, t_row, row, row_ok, n0, half, N);
+      epilogue_columns<BN, false>(ep, fc, t_row, row, row_ok, n0, half, N);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[buf], 0));
@@ -1159,7 +1289,7 @@ static int launch_gemm_impl(const void* A, int lda, const void* B, int ldb, cons
   if (!B_MN) {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
     const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
-    const uint32_t box[2] = {kBK, BN};
+    const uint32_t box[2] = {kBK, ep.mode == kEpiSwiGLU ? 128u : static_cast<uint32_t>(BN)};
     rc = make_tmap_bf16(&tb, B, 2, dims, strides, box);
   } else {
     const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
@@ -1186,8 +1316,8 @@ static int launch_gemm_impl(const void* A, int lda, const void* B, int ldb, cons
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int launch_gemm(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
                        int M, int N, int K, int* status, cudaStream_t stream) {
-  if (fc.rs_mode != 0 || fc.ag_copy_ctas > 0) {
-    // the fused collectives exist for K-major A only (checked by the caller)
+  if (fc.rs_mode != 0 || fc.ag_copy_ctas > 0 || ep.mode >= kEpiRope) {
+    // the fused collectives and the rotary / SwiGLU epilogues exist for K-major A only
     if constexpr (!A_MN)
       return launch_gemm_impl<BN, STAGES, A_MN, B_MN, true>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
     else
@@ -1199,7 +1329,8 @@ static int launch_gemm(const void* A, int lda, const void* B, int ldb, const Gem
 template <bool A_MN, bool B_MN>
 static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
                          int M, int N, int K, int* status, cudaStream_t stream) {
-  if (g_pair_enabled && fc.ag_copy_ctas == 0 && fc.rs_mode == 0 && N >= 256) {
+  if (ep.mode == kEpiSwiGLU) return launch_gemm<256, 4, A_MN, B_MN>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
+  if (g_pair_enabled && fc.ag_copy_ctas == 0 && fc.rs_mode == 0 && N >= 256 && ep.mode < kEpiRope) {
     const int pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
     if (pair_tiles * 3 >= sm_count() / 2)
       return launch_gemm_pair<A_MN, B_MN>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
@@ -1284,7 +1415,7 @@ extern "C" int nmb_gemm_set_pair(int enabled) {
 static int gemm_entry(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc, int M,
                       int N, int K, const void* bias, const void* residual, int ldr, void* aux_out,
                       const void* aux_in, int ld_aux, int mode, int accumulate, int out_f32, float alpha,
-                      const nmb::FusedComm& fc, int* status, void* stream) {
+                      const nmb::FusedComm& fc, const nmb::NmbEpilogueExtra* extra, int* status, void* stream) {
   using namespace nmb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   (void)cudaGetLastError();  // a stale error of this host thread is not ours to report
@@ -1303,6 +1434,30 @@ static int gemm_entry(const void* A, int lda, int a_mn, const void* B, int ldb, 
   ep.accumulate = accumulate;
   ep.out_f32 = out_f32;
   ep.alpha = alpha;
+  ep.rope_table = extra != nullptr ? static_cast<const float2*>(extra->rope_table) : nullptr;
+  ep.rope_pos = extra != nullptr ? extra->rope_pos : nullptr;
+  ep.rope_cols = extra != nullptr ? extra->rope_cols : 0;
+  ep.rope_half = extra != nullptr ? extra->rope_half : 0;
+  ep.swiglu_f = extra != nullptr ? extra->swiglu_f : 0;
+  if (mode == kEpiRope) {
+    // whole 32-column chunks inside one head, 16-byte aligned table rows
+    if (ep.rope_table == nullptr || ep.rope_pos == nullptr || ep.rope_half < 16 || (ep.rope_half % 16) != 0 ||
+        (ep.rope_cols % (2 * ep.rope_half)) != 0 || ep.rope_cols > N || (N % 32) != 0 || out_f32 || accumulate ||
+        (reinterpret_cast<uintptr_t>(ep.rope_table) & 15))
+      return kBadArgument;
+  }
+  if (mode == kEpiSwiGLU) {
+    // N = 2F rows of B = [gate; up]; C is [M, F], aux_out [M, 2F]
+    if (ep.swiglu_f <= 0 || N != 2 * ep.swiglu_f || (ep.swiglu_f % 32) != 0 || a_mn || b_mn || aux_out == nullptr ||
+        out_f32 || accumulate || residual != nullptr || fc.rs_mode != 0)
+      return kBadArgument;
+  }
+  if (mode == kEpiDSwiGLU) {
+    // N = F; C is [M, 2F] (d gate | d up), aux_in [M, 2F]
+    if (ep.swiglu_f != N || (N % 32) != 0 || aux_in == nullptr || out_f32 || accumulate || residual != nullptr ||
+        bias != nullptr || fc.rs_mode != 0)
+      return kBadArgument;
+  }
   const int celt = out_f32 ? 4 : 8;
   if (fc.rs_mode == 0 && ((ldc % celt) != 0 || (reinterpret_cast<uintptr_t>(C) & 15))) return kBadArgument;
   if (residual != nullptr && ((ldr % 8) != 0 || (reinterpret_cast<uintptr_t>(residual) & 15))) return kBadArgument;
@@ -1334,11 +1489,11 @@ extern "C" int nmb_gemm_bf16(const void* A, int lda, int a_mn, const void* B, in
                              void* C, int ldc, int M, int N, int K, const void* bias,
                              const void* residual, int ldr, void* aux_out, const void* aux_in,
                              int ld_aux, int mode, int accumulate, int out_f32, float alpha,
-                             int* status, void* stream) {
+                             const void* extra, int* status, void* stream) {
   nmb::FusedComm fc;
   memset(&fc, 0, sizeof(fc));
   return gemm_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, bias, residual, ldr, aux_out, aux_in, ld_aux, mode,
-                    accumulate, out_f32, alpha, fc, status, stream);
+                    accumulate, out_f32, alpha, fc, static_cast<const nmb::NmbEpilogueExtra*>(extra), status, stream);
 }
 
 // The same GEMM with a collective fused in (see FusedComm).  `comm` has the
@@ -1346,11 +1501,13 @@ extern "C" int nmb_gemm_bf16(const void* A, int lda, int a_mn, const void* B, in
 // of each row block after the reduction (comm->rs_bias / rs_residual).
 extern "C" int nmb_gemm_bf16_fused(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C,
                                    int ldc, int M, int N, int K, const void* bias, void* aux_out,
-                                   int mode, float alpha, const void* comm, int* status, void* stream) {
+                                   int mode, float alpha, const void* comm, const void* extra, int* status,
+                                   void* stream) {
   const nmb::FusedComm* fc = static_cast<const nmb::FusedComm*>(comm);
   const bool rs = fc->rs_mode != 0;
   return gemm_entry(A, lda, a_mn, B, ldb, b_mn, C, ldc, M, N, K, rs ? nullptr : bias, nullptr, 0,
-                    rs ? nullptr : aux_out, nullptr, N, rs ? nmb::kEpiPlain : mode, 0, 0, alpha, *fc, status, stream);
+                    rs ? nullptr : aux_out, nullptr, mode == nmb::kEpiSwiGLU ? N : N, rs ? nmb::kEpiPlain : mode, 0, 0,
+                    alpha, *fc, static_cast<const nmb::NmbEpilogueExtra*>(extra), status, stream);
 }
 
 extern "C" int nmb_fused_max_tiles() { return nmb::kMaxFusedTiles; }

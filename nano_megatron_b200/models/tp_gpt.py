@@ -165,16 +165,40 @@ class TPCausalSelfAttention(nn.Module):
             context = unfused_causal_attention(q, k, v, scale=self.scale)
         return self.out_proj(self._merge_heads(context), residual=residual)
 
+    def _rope_spec(self, device: torch.device, positions: Tensor, rope_cols: int):
+        """Table of (cos, sin) per position and pair, cached per device, plus the
+        flattened positions of this call."""
+        from ..ops.gemm import RopeSpec
+        table = getattr(self, "_rope_table", None)
+        if table is None or table.device != device:
+            half = torch.arange(0, self.config.rotary_dim, 2, device=device).float() / self.config.rotary_dim
+            inv_freq = 1.0 / (float(self.config.rotary_base) ** half)
+            table = RopeSpec.make_table(inv_freq, self.config.max_seq_len)
+            self._rope_table = table
+        pos = positions.contiguous()
+        if pos.dtype != torch.long:
+            pos = pos.long()
+        return RopeSpec(table, pos, rope_cols)
+
     def _forward_native(self, x: Tensor, positions: Optional[Tensor], residual: Optional[Tensor]) -> Tensor:
         """bf16 GPU path: packed projection -> in-place views -> tcgen05 attention."""
         from ..ops.attention import flash_attention, flash_attention_packed, split_packed_qkv
 
         d = self.head_dim
         hq, hkv = self.local_num_heads, self.local_num_kv_heads
+        rotate = self.rotary_emb and positions is not None
         if self.config.use_fused_qkv:
+            if rotate and self._cp_size == 1 and d % 32 == 0 and self.config.rotary_dim == d:
+                # rotary embedding in the projection's epilogue, undone inside the attention
+                # backward: no rotation kernel, and the packed layout is kept
+                spec = self._rope_spec(x.device, positions, (hq + hkv) * d)
+                qkv = self.qkv_proj(x, rope=spec)
+                b, s, _ = qkv.shape
+                context = flash_attention_packed(qkv.contiguous(), hq, hkv, d, self.scale, rope=spec)
+                return self.out_proj(context.view(b, s, hq * d), residual=residual)
             qkv = self.qkv_proj(x)
             b, s, _ = qkv.shape
-            if self._cp_size == 1 and not (self.rotary_emb and positions is not None) and qkv.is_contiguous():
+            if self._cp_size == 1 and not rotate and qkv.is_contiguous():
                 context = flash_attention_packed(qkv, hq, hkv, d, self.scale)
                 return self.out_proj(context.view(b, s, hq * d), residual=residual)
             q, k, v = split_packed_qkv(qkv, hq, hkv, d)
@@ -216,6 +240,10 @@ class TPMLP(nn.Module):
 
     def forward(self, x: Tensor, *, residual: Optional[Tensor] = None) -> Tensor:
         if self.config.gated_linear_unit:
+            if OF.native_linear_ok(x, self.fc1.weight) and OF.swiglu_epilogue_ok(self.fc1.weight):
+                # silu(gate) * up in the fc1 epilogue, its backward in the fc2 dgrad epilogue
+                pre, act = self.fc1(x, split_act="swiglu")
+                return self.fc2(act, residual=residual, act_pre=pre, act="swiglu")
             return self.fc2(OF.swiglu(self.fc1(x)), residual=residual)
         pre, act = self.fc1(x, split_gelu=True)
         return self.fc2(act, residual=residual, gelu_pre=pre)

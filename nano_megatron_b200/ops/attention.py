@@ -58,12 +58,15 @@ def attn_fwd(q, k_chunks, v_chunks, scale: float, q_pos0: int = 0):
 def attn_bwd(q, k_chunks, v_chunks, out, dout, lse, scale: float, q_pos0: int = 0,
              dk_chunks: Optional[Sequence[torch.Tensor]] = None,
              dv_chunks: Optional[Sequence[torch.Tensor]] = None,
-             dq: Optional[torch.Tensor] = None):
+             dq: Optional[torch.Tensor] = None, rope=None):
     """Returns ``(dq, dk_chunks, dv_chunks)``.  ``dk_chunks[c]`` receives this
     rank's contribution to chunk ``c``; rows of chunks the queries cannot see
     are left untouched (callers pass zero-filled or freshly visible buffers).
     ``dq`` / ``dk_chunks`` / ``dv_chunks`` may be strided views (for instance
-    slices of one packed dQKV buffer); they are written in place."""
+    slices of one packed dQKV buffer); they are written in place.  With
+    ``rope`` (a ``RopeSpec``: q and k were rotated by the projection's epilogue)
+    dq and dk come back un-rotated, i.e. as gradients of the projection output;
+    that needs a single key chunk as long as the query sequence."""
     b, sq, hq, d = q.shape
     chunk_len, hkv = k_chunks[0].shape[1], k_chunks[0].shape[2]
     n_chunks = len(k_chunks)
@@ -87,6 +90,8 @@ def attn_bwd(q, k_chunks, v_chunks, out, dout, lse, scale: float, q_pos0: int = 
         native.ptr(dq_acc), ctypes.byref(dqd), _desc_array(dk_chunks), _desc_array(dv_chunks),
         ctypes.c_int(b), ctypes.c_int(hq), ctypes.c_int(hkv), ctypes.c_int(sq), ctypes.c_int(d),
         ctypes.c_int(q_pos0), ctypes.c_int(n_tiles), ctypes.c_float(scale),
+        native.ptr(rope.table if rope is not None else None),
+        native.ptr(rope.positions if rope is not None else None),
         native.ptr(native.status_word(q.device)), native.stream_ptr(q.device))
     native.check_rc(rc, "nmb_attn_bwd")
     return dq, list(dk_chunks), list(dv_chunks)
@@ -127,29 +132,36 @@ class _FlashAttentionPacked(torch.autograd.Function):
     slice-gradient zero-fill / copy / add kernels run around the attention."""
 
     @staticmethod
-    def forward(ctx, qkv, hq, hkv, d, scale):
+    def forward(ctx, qkv, hq, hkv, d, scale, rope=None):
         q, k, v = _split_packed(qkv, hq, hkv, d)
         out, lse = attn_fwd(q, [k], [v], scale, 0)
         ctx.save_for_backward(qkv, out, lse)
-        ctx.meta = (hq, hkv, d, scale)
+        ctx.meta = (hq, hkv, d, scale, rope)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         qkv, out, lse = ctx.saved_tensors
-        hq, hkv, d, scale = ctx.meta
+        hq, hkv, d, scale, rope = ctx.meta
         q, k, v = _split_packed(qkv, hq, hkv, d)
         dqkv = torch.empty_like(qkv)
         dq, dk, dv = _split_packed(dqkv, hq, hkv, d)
-        attn_bwd(q, [k], [v], out, dout, lse, scale, 0, dk_chunks=[dk], dv_chunks=[dv], dq=dq)
-        return dqkv, None, None, None, None
+        attn_bwd(q, [k], [v], out, dout, lse, scale, 0, dk_chunks=[dk], dv_chunks=[dv], dq=dq, rope=rope)
+        return dqkv, None, None, None, None, None
 
 
-def flash_attention_packed(qkv: torch.Tensor, hq: int, hkv: int, d: int, scale: float) -> torch.Tensor:
+def flash_attention_packed(qkv: torch.Tensor, hq: int, hkv: int, d: int, scale: float, rope=None) -> torch.Tensor:
     """Causal attention over a packed, contiguous ``[B, S, (Hq + 2 Hkv) d]`` tensor
-    (query heads, then key heads, then value heads); returns ``[B, S, Hq, d]``."""
+    (query heads, then key heads, then value heads); returns ``[B, S, Hq, d]``.
+
+    ``rope``: the q and k slices were rotated by the epilogue of the projection
+    that produced ``qkv`` (``linear(..., rope=spec)``).  The forward pass is the
+    same; the backward pass un-rotates dq and dk inside its last kernel, so the
+    gradient returned for ``qkv`` is the gradient of the projection's
+    *un-rotated* output and the projection's backward stays a plain linear
+    backward.  The two must be used together."""
     assert qkv.dim() == 3 and qkv.is_contiguous() and qkv.shape[-1] == (hq + 2 * hkv) * d
-    return _FlashAttentionPacked.apply(qkv, hq, hkv, d, float(scale))
+    return _FlashAttentionPacked.apply(qkv, hq, hkv, d, float(scale), rope)
 
 
 class _SplitPacked(torch.autograd.Function):

@@ -26,7 +26,8 @@ import torch.nn.functional as F
 from torch import Tensor
 
 from . import kernels
-from .gemm import EPI_DGELU, EPI_GELU, EPI_PLAIN, gemm_bf16, gemm_supported
+from .gemm import (EPI_DGELU, EPI_DSWIGLU, EPI_GELU, EPI_PLAIN, EPI_ROPE, EPI_SWIGLU, RopeSpec, gemm_bf16,
+                   gemm_supported)
 
 
 def use_native(t: Tensor) -> bool:
@@ -53,7 +54,8 @@ class _LinearFn(torch.autograd.Function):
     """y = act(x W^T + b) (+ residual) on the tcgen05 GEMM."""
 
     @staticmethod
-    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor], gelu: bool):
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor], gelu: bool,
+                rope: Optional[RopeSpec] = None):
         x2 = x.reshape(-1, x.shape[-1])
         if x2.stride(-1) != 1 or (x2.stride(0) % 8) != 0:
             x2 = x2.contiguous()
@@ -63,6 +65,11 @@ class _LinearFn(torch.autograd.Function):
         if gelu:
             pre = torch.empty((x2.shape[0], n), dtype=torch.bfloat16, device=x.device)
             y = gemm_bf16(x2, weight, bias=bias, mode=EPI_GELU, aux_out=pre)
+        elif rope is not None:
+            # q and k heads leave the projection already rotated; the attention
+            # backward hands back the gradient of the un-rotated output, so the
+            # backward below is the plain linear one
+            y = gemm_bf16(x2, weight, bias=bias, mode=EPI_ROPE, rope=rope)
         else:
             y = gemm_bf16(x2, weight, bias=bias, residual=res2, mode=EPI_PLAIN)
         ctx.save_for_backward(x2, weight, pre)
@@ -94,7 +101,7 @@ class _LinearFn(torch.autograd.Function):
         db = None
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dz, out=out, accumulate=acc))
-        return dx, dw, db, d_res, None
+        return dx, dw, db, d_res, None, None
 
 
 def _rows(t: Tensor, width: int) -> Tensor:
@@ -104,81 +111,101 @@ def _rows(t: Tensor, width: int) -> Tensor:
     return t2
 
 
-class _LinearGeluSplitFn(torch.autograd.Function):
-    """First MLP GEMM: returns the pre-activation (differentiable) and its GELU
-    (a side output written by the same epilogue)."""
+class _LinearActSplitFn(torch.autograd.Function):
+    """First MLP GEMM: returns the pre-activation (differentiable) and its
+    activation (a side output written by the same epilogue).  ``act`` is
+    ``"gelu"`` (pre and activation both ``[.., F]``) or ``"swiglu"`` (weight rows
+    ``[gate; up]``, pre ``[.., 2F]``, activation ``silu(gate) * up`` ``[.., F]``)."""
 
     @staticmethod
-    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor]):
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], act: str):
         x2 = _rows(x, x.shape[-1])
         n = weight.shape[0]
         pre = torch.empty((x2.shape[0], n), dtype=torch.bfloat16, device=x.device)
-        act = gemm_bf16(x2, weight, bias=bias, mode=EPI_GELU, aux_out=pre)
+        out = gemm_bf16(x2, weight, bias=bias, mode=EPI_SWIGLU if act == "swiglu" else EPI_GELU, aux_out=pre)
         ctx.save_for_backward(x2, weight)
         ctx.params = (weight, bias)
         ctx.in_shape = x.shape
-        out_shape = (*x.shape[:-1], n)
-        act = act.view(out_shape)
-        ctx.mark_non_differentiable(act)
+        out = out.view(*x.shape[:-1], out.shape[-1])
+        ctx.mark_non_differentiable(out)
         # no zero-filled gradient tensor for the non-differentiable side output
         ctx.set_materialize_grads(False)
-        return pre.view(out_shape), act
+        return pre.view(*x.shape[:-1], n), out
 
     @staticmethod
     def backward(ctx, dpre: Optional[Tensor], _dact):
         x2, weight = ctx.saved_tensors
         w_param, b_param = ctx.params
         if dpre is None:
-            return None, None, None
+            return None, None, None, None
         dz = _rows(dpre, weight.shape[0])
         dx = gemm_bf16(dz, weight, b_mn=True).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
         dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dz, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
         db = None
         if b_param is not None:
             db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dz, out=out, accumulate=acc))
-        return dx, dw, db
+        return dx, dw, db, None
 
 
-class _LinearFromGeluFn(torch.autograd.Function):
-    """Second MLP GEMM.  Its input is ``gelu(pre)`` (already computed); the
-    gradient it returns is with respect to ``pre``: GELU' is applied in the
-    epilogue of the dgrad GEMM, so no separate GELU-backward kernel runs."""
+class _LinearFromActFn(torch.autograd.Function):
+    """Second MLP GEMM.  Its input is ``act(pre)`` (already computed); the
+    gradient it returns is with respect to ``pre``: GELU' / the SwiGLU backward
+    is applied in the epilogue of the dgrad GEMM, so no separate
+    activation-backward kernel runs."""
 
     @staticmethod
-    def forward(ctx, pre: Tensor, act: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor]):
-        k = act.shape[-1]
-        a2 = _rows(act, k)
+    def forward(ctx, pre: Tensor, act_t: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor],
+                act: str):
+        k = act_t.shape[-1]
+        a2 = _rows(act_t, k)
         n = weight.shape[0]
         res2 = residual.reshape(-1, n) if residual is not None else None
         y = gemm_bf16(a2, weight, bias=bias, residual=res2)
-        ctx.save_for_backward(_rows(pre, k), a2, weight)
+        ctx.save_for_backward(_rows(pre, pre.shape[-1]), a2, weight)
         ctx.params = (weight, bias)
-        ctx.has_res = residual is not None
-        ctx.pre_shape = pre.shape
-        return y.view(*act.shape[:-1], n)
+        ctx.meta = (residual is not None, pre.shape, act)
+        return y.view(*act_t.shape[:-1], n)
 
     @staticmethod
     def backward(ctx, dy: Tensor):
         pre2, a2, weight = ctx.saved_tensors
         w_param, b_param = ctx.params
+        has_res, pre_shape, act = ctx.meta
         dy2 = _rows(dy, weight.shape[0])
-        dpre = gemm_bf16(dy2, weight, b_mn=True, mode=EPI_DGELU, aux_in=pre2).view(ctx.pre_shape)
+        dpre = gemm_bf16(dy2, weight, b_mn=True, mode=EPI_DSWIGLU if act == "swiglu" else EPI_DGELU,
+                         aux_in=pre2).view(pre_shape)
         dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dy2, a2, a_mn=True, b_mn=True, out=out, accumulate=acc))
         db = None
         if b_param is not None:
             db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dy2, out=out, accumulate=acc))
-        return dpre, None, dw, db, (dy if ctx.has_res else None)
+        return dpre, None, dw, db, (dy if has_res else None), None
 
 
 def linear_gelu_split(x: Tensor, weight: Tensor, bias: Optional[Tensor]) -> tuple[Tensor, Tensor]:
     """``pre = x W^T + b`` and ``gelu(pre)`` from one GEMM (native path only)."""
-    return _LinearGeluSplitFn.apply(x, weight, bias)
+    return _LinearActSplitFn.apply(x, weight, bias, "gelu")
+
+
+def linear_act_split(x: Tensor, weight: Tensor, bias: Optional[Tensor], act: str) -> tuple[Tensor, Tensor]:
+    """``pre = x W^T + b`` and ``act(pre)`` from one GEMM (native path only)."""
+    return _LinearActSplitFn.apply(x, weight, bias, act)
 
 
 def linear_from_gelu(pre: Tensor, act: Tensor, weight: Tensor, bias: Optional[Tensor],
                      residual: Optional[Tensor] = None) -> Tensor:
     """``act W^T + b (+ residual)`` where ``act = gelu(pre)``; backward flows into ``pre``."""
-    return _LinearFromGeluFn.apply(pre, act, weight, bias, residual)
+    return _LinearFromActFn.apply(pre, act, weight, bias, residual, "gelu")
+
+
+def linear_from_act(pre: Tensor, act_t: Tensor, weight: Tensor, bias: Optional[Tensor],
+                    residual: Optional[Tensor] = None, act: str = "gelu") -> Tensor:
+    """``act_t W^T + b (+ residual)`` where ``act_t = act(pre)``; backward flows into ``pre``."""
+    return _LinearFromActFn.apply(pre, act_t, weight, bias, residual, act)
+
+
+def swiglu_epilogue_ok(weight: Tensor) -> bool:
+    """The fused SwiGLU epilogue needs whole 32-column chunks of gate / up."""
+    return weight.shape[0] % 64 == 0
 
 
 def native_linear_ok(x: Tensor, weight: Tensor) -> bool:
@@ -189,11 +216,13 @@ def native_linear_ok(x: Tensor, weight: Tensor) -> bool:
 
 
 def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, *, residual: Optional[Tensor] = None,
-           gelu: bool = False) -> Tensor:
-    """``act(x @ weight.T + bias) + residual`` (``gelu`` and ``residual`` are exclusive)."""
+           gelu: bool = False, rope: Optional[RopeSpec] = None) -> Tensor:
+    """``act(x @ weight.T + bias) + residual`` (``gelu`` and ``residual`` are exclusive).
+    ``rope`` (native path only) rotates the leading q / k columns in the epilogue."""
     assert not (gelu and residual is not None)
     if native_linear_ok(x, weight):
-        return _LinearFn.apply(x, weight, bias, residual, gelu)
+        return _LinearFn.apply(x, weight, bias, residual, gelu, rope)
+    assert rope is None, "the rotary epilogue exists on the native path only"
     # Rows that are not multiples of 16 bytes cannot be described to TMA; such
     # (toy) shapes use the PyTorch expression below.
     y = F.linear(x, weight, bias)

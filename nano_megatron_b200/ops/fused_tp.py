@@ -33,7 +33,8 @@ from torch import Tensor
 
 from . import kernels, native
 from .functional import _deliver_grad
-from .gemm import EPI_DGELU, EPI_GELU, EPI_PLAIN, gemm_bf16
+from .gemm import (EPI_DGELU, EPI_DSWIGLU, EPI_GELU, EPI_PLAIN, EPI_ROPE, EPI_SWIGLU, RopeSpec, epilogue_extra,
+                   gemm_bf16)
 from ..utils.tracing import nvtx_range
 
 _MAX = 8
@@ -154,14 +155,16 @@ class TPFused:
 
     # -- launches ----------------------------------------------------------------
     def _launch(self, a: Tensor, b: Tensor, b_mn: bool, out: Optional[Tensor], m: int, n: int, k: int,
-                bias: Optional[Tensor], aux_out: Optional[Tensor], mode: int, fc: _FusedComm) -> None:
+                bias: Optional[Tensor], aux_out: Optional[Tensor], mode: int, fc: _FusedComm,
+                rope: Optional[RopeSpec] = None) -> None:
         status = native.status_word(a.device)
+        extra = epilogue_extra(rope if mode == EPI_ROPE else None, n // 2 if mode == EPI_SWIGLU else 0)
         rc = native.lib().nmb_gemm_bf16_fused(
             native.ptr(a), ctypes.c_int(a.stride(0)), ctypes.c_int(0), native.ptr(b), ctypes.c_int(b.stride(0)),
             ctypes.c_int(int(b_mn)), native.ptr(out), ctypes.c_int(out.stride(0) if out is not None else n),
             ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k), native.ptr(bias), native.ptr(aux_out),
-            ctypes.c_int(mode), ctypes.c_float(1.0), ctypes.byref(fc), native.ptr(status),
-            native.stream_ptr(a.device))
+            ctypes.c_int(mode), ctypes.c_float(1.0), ctypes.byref(fc),
+            ctypes.byref(extra) if extra is not None else None, native.ptr(status), native.stream_ptr(a.device))
         native.check_rc(rc, "nmb_gemm_bf16_fused")
 
     def gemm_reduce_scatter(self, a: Tensor, b: Tensor, seq_len: int, *, b_mn: bool = False,
@@ -221,12 +224,12 @@ class TPFused:
 
     def allgather_gemm(self, full: Tensor, b: Tensor, seq_len: int, *, b_mn: bool = False,
                        bias: Optional[Tensor] = None, mode: int = EPI_PLAIN,
-                       aux_out: Optional[Tensor] = None) -> Tensor:
+                       aux_out: Optional[Tensor] = None, rope: Optional[RopeSpec] = None) -> Tensor:
         """``full @ B^T`` where only this rank's sequence shard of the symmetric
         buffer ``full`` is valid on entry; on return ``full`` holds every shard."""
         m, k = full.shape
         n = b.shape[1] if b_mn else b.shape[0]
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=full.device)
+        out = torch.empty((m, n // 2 if mode == EPI_SWIGLU else n), dtype=torch.bfloat16, device=full.device)
         fc = self._base(seq_len, m)
         fc.ag_copy_ctas = COPY_CTAS
         fc.ag_dst = full.data_ptr()
@@ -234,7 +237,7 @@ class TPFused:
         for i, p in enumerate(self.ws.peers_of(full)):
             fc.ag_src[i] = p
         with nvtx_range("allgather_gemm"):
-            self._launch(full, b, b_mn, out, m, n, k, bias, aux_out, mode, fc)
+            self._launch(full, b, b_mn, out, m, n, k, bias, aux_out, mode, fc, rope)
         STATS["allgather_gemm"] += 1
         # bytes the copy CTAs pull from the peers' shards
         STATS["nvlink_bytes"] += m * k * 2 * (self.ws.size - 1) // self.ws.size
@@ -261,32 +264,43 @@ def _place_shard(full: Tensor, shard: Tensor, rank: int, seq_len: int, size: int
     full.view(b, seq_len, -1)[:, rank * width:(rank + 1) * width].copy_(shard.reshape(b, width, -1))
 
 
+def _act_mode(act: Optional[str], rope: Optional[RopeSpec]) -> int:
+    if act == "swiglu":
+        return EPI_SWIGLU
+    if act == "gelu":
+        return EPI_GELU
+    return EPI_ROPE if rope is not None else EPI_PLAIN
+
+
 class _SPColumnLinearFn(torch.autograd.Function):
-    """Sequence-parallel column linear: all-gather -> GEMM (+bias, +GELU split)."""
+    """Sequence-parallel column linear: all-gather -> GEMM (+bias, + activation
+    split or rotary epilogue).  With ``act`` it returns ``(pre, act(pre))``."""
 
     @staticmethod
     def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], st: TPFused, seq_len: int, site: Any,
-                split_gelu: bool):
+                act: Optional[str], rope: Optional[RopeSpec] = None):
         bsz, width, k = x.shape
         rows = bsz * seq_len
         full = st.gather_buffer(rows, k, owner=site)
         _place_shard(full, x, st.ws.rank, seq_len, st.ws.size)
         n = weight.shape[0]
-        pre = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device) if split_gelu else None
-        y = st.allgather_gemm(full, weight, seq_len, bias=bias, mode=EPI_GELU if split_gelu else EPI_PLAIN,
-                              aux_out=pre)
+        pre = torch.empty((rows, n), dtype=torch.bfloat16, device=x.device) if act else None
+        y = st.allgather_gemm(full, weight, seq_len, bias=bias, mode=_act_mode(act, rope), aux_out=pre, rope=rope)
         ctx.save_for_backward(full, weight)
         ctx.meta = (st, seq_len, (weight, bias), x.shape)
-        if split_gelu:
-            y = y.view(bsz, seq_len, n)
+        if act:
+            y = y.view(bsz, seq_len, y.shape[-1])
             ctx.mark_non_differentiable(y)
+            ctx.set_materialize_grads(False)
             return pre.view(bsz, seq_len, n), y
         return y.view(bsz, seq_len, n)
 
     @staticmethod
-    def backward(ctx, dy: Tensor, *_unused):
+    def backward(ctx, dy: Optional[Tensor], *_unused):
         full, weight = ctx.saved_tensors
         st, seq_len, (w_param, b_param), in_shape = ctx.meta
+        if dy is None:
+            return (None,) * 8
         n = weight.shape[0]
         dz = dy.reshape(-1, n)
         if dz.stride(-1) != 1 or dz.stride(0) % 8 != 0:
@@ -297,7 +311,7 @@ class _SPColumnLinearFn(torch.autograd.Function):
         db = None
         if b_param is not None:
             db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dz, out=out, accumulate=acc))
-        return dx, dw, db, None, None, None, None
+        return dx, dw, db, None, None, None, None, None
 
 
 class _SPRowLinearFn(torch.autograd.Function):
@@ -305,7 +319,7 @@ class _SPRowLinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor],
-                gelu_pre: Optional[Tensor], st: TPFused, seq_len: int):
+                gelu_pre: Optional[Tensor], st: TPFused, seq_len: int, act: str = "gelu"):
         bsz, s, k = x.shape
         x2 = x.reshape(-1, k)
         if x2.stride(-1) != 1 or x2.stride(0) % 8 != 0:
@@ -313,24 +327,24 @@ class _SPRowLinearFn(torch.autograd.Function):
         n = weight.shape[0]
         res2 = residual.reshape(-1, n).contiguous() if residual is not None else None
         out = st.gemm_reduce_scatter(x2, weight, seq_len, bias=bias, residual=res2)
-        pre2 = gelu_pre.reshape(-1, k) if gelu_pre is not None else None
+        pre2 = gelu_pre.reshape(-1, gelu_pre.shape[-1]) if gelu_pre is not None else None
         ctx.save_for_backward(x2, weight, pre2)
-        ctx.meta = (st, seq_len, (weight, bias), x.shape, residual is not None)
+        ctx.meta = (st, seq_len, (weight, bias), x.shape, residual is not None, act,
+                    gelu_pre.shape if gelu_pre is not None else None)
         return out.view(bsz, seq_len // st.ws.size, n)
 
     @staticmethod
     def backward(ctx, dy: Tensor):
         x2, weight, pre2 = ctx.saved_tensors
-        st, seq_len, (w_param, b_param), in_shape, has_res = ctx.meta
+        st, seq_len, (w_param, b_param), in_shape, has_res, act, pre_shape = ctx.meta
         n = weight.shape[0]
         rows = x2.shape[0]
-        # all-gather dY, then dgrad (with GELU' folded in when the input was a GELU)
+        # all-gather dY, then dgrad, then the activation's backward on the pre-activation
         dy_full = st.gather_buffer(rows, n)
         _place_shard(dy_full, dy, st.ws.rank, seq_len, st.ws.size)
         if pre2 is not None:
-            # dgrad epilogue needs the pre-activation: plain fused GEMM, then GELU'
             dact = st.allgather_gemm(dy_full, weight, seq_len, b_mn=True)
-            dx = kernels.gelu_bwd(pre2, dact)
+            dx = kernels.swiglu_bwd(pre2, dact) if act == "swiglu" else kernels.gelu_bwd(pre2, dact)
         else:
             dx = st.allgather_gemm(dy_full, weight, seq_len, b_mn=True)
         dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dy_full, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
@@ -339,10 +353,9 @@ class _SPRowLinearFn(torch.autograd.Function):
             dyl = dy.reshape(-1, n)
             dyl = dyl if dyl.is_contiguous() else dyl.contiguous()
             db = kernels.col_sum(dyl)  # partial over this rank's tokens; summed over TP by the SP grad hook
-        d_pre = dx.view(in_shape)
         if pre2 is not None:
-            return None, dw, db, (dy if has_res else None), d_pre, None, None
-        return d_pre, dw, db, (dy if has_res else None), None, None, None
+            return None, dw, db, (dy if has_res else None), dx.view(pre_shape), None, None, None
+        return dx.view(in_shape), dw, db, (dy if has_res else None), None, None, None, None
 
 
 class _TPColumnLinearFn(torch.autograd.Function):
@@ -352,7 +365,8 @@ class _TPColumnLinearFn(torch.autograd.Function):
     (the reference's ``_CopyToTPRegion`` backward, nano_megatron/parallel/mappings.py:242-257)."""
 
     @staticmethod
-    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], st: TPFused, split_gelu: bool):
+    def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], st: TPFused, act: Optional[str],
+                rope: Optional[RopeSpec] = None):
         k = x.shape[-1]
         x2 = x.reshape(-1, k)
         if x2.stride(-1) != 1 or x2.stride(0) % 8 != 0:
@@ -361,20 +375,21 @@ class _TPColumnLinearFn(torch.autograd.Function):
         ctx.save_for_backward(x2, weight)
         ctx.meta = (st, (weight, bias), x.shape)
         out_shape = (*x.shape[:-1], n)
-        if split_gelu:
+        if act:
             pre = torch.empty((x2.shape[0], n), dtype=torch.bfloat16, device=x.device)
-            act = gemm_bf16(x2, weight, bias=bias, mode=EPI_GELU, aux_out=pre).view(out_shape)
-            ctx.mark_non_differentiable(act)
+            y = gemm_bf16(x2, weight, bias=bias, mode=_act_mode(act, None), aux_out=pre)
+            y = y.view(*x.shape[:-1], y.shape[-1])
+            ctx.mark_non_differentiable(y)
             ctx.set_materialize_grads(False)
-            return pre.view(out_shape), act
-        return gemm_bf16(x2, weight, bias=bias).view(out_shape)
+            return pre.view(out_shape), y
+        return gemm_bf16(x2, weight, bias=bias, mode=_act_mode(None, rope), rope=rope).view(out_shape)
 
     @staticmethod
     def backward(ctx, dy: Optional[Tensor], *_unused):
         x2, weight = ctx.saved_tensors
         st, (w_param, b_param), in_shape = ctx.meta
         if dy is None:
-            return None, None, None, None, None
+            return None, None, None, None, None, None
         n = weight.shape[0]
         dz = dy.reshape(-1, n)
         if dz.stride(-1) != 1 or dz.stride(0) % 8 != 0:
@@ -384,7 +399,7 @@ class _TPColumnLinearFn(torch.autograd.Function):
         db = None
         if b_param is not None:
             db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dz, out=out, accumulate=acc))
-        return dx, dw, db, None, None
+        return dx, dw, db, None, None, None
 
 
 class _TPRowLinearFn(torch.autograd.Function):
@@ -395,7 +410,7 @@ class _TPRowLinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor],
-                gelu_pre: Optional[Tensor], st: TPFused):
+                gelu_pre: Optional[Tensor], st: TPFused, act: str = "gelu"):
         k = x.shape[-1]
         x2 = x.reshape(-1, k)
         if x2.stride(-1) != 1 or x2.stride(0) % 8 != 0:
@@ -403,21 +418,23 @@ class _TPRowLinearFn(torch.autograd.Function):
         n = weight.shape[0]
         res2 = residual.reshape(-1, n).contiguous() if residual is not None else None
         out = st.gemm_all_reduce(x2, weight, bias=bias, residual=res2)
-        pre2 = gelu_pre.reshape(-1, k) if gelu_pre is not None else None
+        pre2 = gelu_pre.reshape(-1, gelu_pre.shape[-1]) if gelu_pre is not None else None
         ctx.save_for_backward(x2, weight, pre2)
-        ctx.meta = ((weight, bias), x.shape, residual is not None)
+        ctx.meta = ((weight, bias), x.shape, residual is not None, act,
+                    gelu_pre.shape if gelu_pre is not None else None)
         return out.view(*x.shape[:-1], n)
 
     @staticmethod
     def backward(ctx, dy: Tensor):
         x2, weight, pre2 = ctx.saved_tensors
-        (w_param, b_param), in_shape, has_res = ctx.meta
+        (w_param, b_param), in_shape, has_res, act, pre_shape = ctx.meta
         n = weight.shape[0]
         dy2 = dy.reshape(-1, n)
         if dy2.stride(-1) != 1 or dy2.stride(0) % 8 != 0:
             dy2 = dy2.contiguous()
         if pre2 is not None:
-            dx = gemm_bf16(dy2, weight, b_mn=True, mode=EPI_DGELU, aux_in=pre2).view(in_shape)
+            dx = gemm_bf16(dy2, weight, b_mn=True, mode=EPI_DSWIGLU if act == "swiglu" else EPI_DGELU,
+                           aux_in=pre2).view(pre_shape)
         else:
             dx = gemm_bf16(dy2, weight, b_mn=True).view(in_shape)
         dw = _deliver_grad(w_param, lambda out, acc: gemm_bf16(dy2, x2, a_mn=True, b_mn=True, out=out, accumulate=acc))
@@ -427,5 +444,5 @@ class _TPRowLinearFn(torch.autograd.Function):
             db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dy2, out=out, accumulate=acc))
         d_res = dy if has_res else None
         if pre2 is not None:
-            return None, dw, db, d_res, dx, None
-        return dx, dw, db, d_res, None, None
+            return None, dw, db, d_res, dx, None, None
+        return dx, dw, db, d_res, None, None, None

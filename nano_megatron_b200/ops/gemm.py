@@ -9,13 +9,56 @@ transposed copies.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
 
 from . import native
 
-EPI_PLAIN, EPI_GELU, EPI_DGELU = 0, 1, 2
+EPI_PLAIN, EPI_GELU, EPI_DGELU, EPI_ROPE, EPI_SWIGLU, EPI_DSWIGLU = 0, 1, 2, 3, 4, 5
+
+
+class _EpilogueExtra(ctypes.Structure):
+    _fields_ = [("rope_table", ctypes.c_void_p), ("rope_pos", ctypes.c_void_p), ("rope_cols", ctypes.c_int),
+                ("rope_half", ctypes.c_int), ("swiglu_f", ctypes.c_int)]
+
+
+@dataclass
+class RopeSpec:
+    """Rotary embedding applied by a GEMM epilogue (and undone by the attention
+    backward): ``table[p, i] = (cos, sin)`` of position ``p`` times inverse
+    frequency ``i`` (fp32, ``[positions, head_dim / 2, 2]``), ``positions`` the
+    position of every output row (int64, ``rows`` long when flattened), and the
+    number of leading output columns that hold rotated heads (q and k)."""
+
+    table: torch.Tensor
+    positions: torch.Tensor
+    rope_cols: int
+
+    @property
+    def half(self) -> int:
+        return self.table.shape[1]
+
+    @staticmethod
+    def make_table(inv_freq: torch.Tensor, max_positions: int) -> torch.Tensor:
+        ang = torch.outer(torch.arange(max_positions, device=inv_freq.device, dtype=torch.float32),
+                          inv_freq.to(torch.float32))
+        return torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous()
+
+
+def epilogue_extra(rope: Optional[RopeSpec] = None, swiglu_f: int = 0):
+    """ctypes argument for the optional epilogue parameters (``None`` when unused)."""
+    if rope is None and not swiglu_f:
+        return None
+    ex = _EpilogueExtra()
+    if rope is not None:
+        assert rope.table.dtype == torch.float32 and rope.table.is_contiguous()
+        assert rope.positions.dtype == torch.long and rope.positions.is_contiguous()
+        ex.rope_table, ex.rope_pos = rope.table.data_ptr(), rope.positions.data_ptr()
+        ex.rope_cols, ex.rope_half = int(rope.rope_cols), int(rope.half)
+    ex.swiglu_f = int(swiglu_f)
+    return ex
 
 
 def _as_2d(t: torch.Tensor) -> torch.Tensor:
@@ -46,6 +89,8 @@ def gemm_bf16(
     accumulate: bool = False,
     out_dtype: torch.dtype = torch.bfloat16,
     alpha: float = 1.0,
+    rope: Optional[RopeSpec] = None,
+    swiglu_f: int = 0,
 ) -> torch.Tensor:
     a = _as_2d(a)
     b = _as_2d(b)
@@ -60,19 +105,29 @@ def gemm_bf16(
         n, kb = b.shape
     if k != kb:
         raise ValueError(f"reduction dims differ: {k} vs {kb}")
+    # SwiGLU: the B rows are [gate; up] (n = 2F) and C is [m, F]; its backward
+    # epilogue turns d(act) [m, F] into [d gate | d up] = [m, 2F]
+    out_cols = {EPI_SWIGLU: n // 2, EPI_DSWIGLU: 2 * n}.get(mode, n)
     if out is None:
-        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+        out = torch.empty((m, out_cols), dtype=out_dtype, device=a.device)
     else:
-        assert out.shape == (m, n) and out.stride(1) == 1
+        assert out.shape == (m, out_cols) and out.stride(1) == 1
+    if mode == EPI_SWIGLU:
+        assert aux_out is not None
+        swiglu_f = n // 2
+    elif mode == EPI_DSWIGLU:
+        assert aux_in is not None
+        swiglu_f = n
     if mode == EPI_GELU and aux_out is None:
         aux_out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
     if residual is not None:
         residual = _as_2d(residual)
-    aux = aux_out if mode == EPI_GELU else aux_in
+    aux = aux_out if mode in (EPI_GELU, EPI_SWIGLU) else aux_in
     if aux is not None:
         aux = _as_2d(aux)
     ld_aux = aux.stride(0) if aux is not None else 0
     status = native.status_word(a.device)
+    extra = epilogue_extra(rope if mode == EPI_ROPE else None, swiglu_f)
     rc = native.lib().nmb_gemm_bf16(
         native.ptr(a), ctypes.c_int(a.stride(0)), ctypes.c_int(int(a_mn)),
         native.ptr(b), ctypes.c_int(b.stride(0)), ctypes.c_int(int(b_mn)),
@@ -80,10 +135,11 @@ def gemm_bf16(
         ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k),
         native.ptr(bias), native.ptr(residual),
         ctypes.c_int(residual.stride(0) if residual is not None else 0),
-        native.ptr(aux_out if mode == EPI_GELU else None),
-        native.ptr(aux if mode == EPI_DGELU else None),
+        native.ptr(aux if mode in (EPI_GELU, EPI_SWIGLU) else None),
+        native.ptr(aux if mode in (EPI_DGELU, EPI_DSWIGLU) else None),
         ctypes.c_int(ld_aux), ctypes.c_int(mode), ctypes.c_int(int(accumulate)),
         ctypes.c_int(int(out.dtype == torch.float32)), ctypes.c_float(alpha),
+        ctypes.byref(extra) if extra is not None else None,
         native.ptr(status), native.stream_ptr(a.device),
     )
     native.check_rc(rc, "nmb_gemm_bf16")

@@ -113,6 +113,8 @@ def check_status(device: torch.device | None = None, *, reset: bool = True) -> N
 _KERNELS_PER_CALL = {"nmb_attn_bwd": 3, "nmb_col_reduce": 2, "nmb_adamw_step": 2}
 #: running count of kernels of this library launched (or captured) by this process
 launches = 0
+#: the same per C entry point (tests use it to show that a fused path left no stand-alone kernel behind)
+launch_counts: dict[str, int] = {}
 
 
 def check_rc(rc: int, what: str) -> None:
@@ -120,3 +122,4 @@ def check_rc(rc: int, what: str) -> None:
     if rc != 0:
         raise NativeKernelError(f"{what}: launcher returned {rc}")
     launches += _KERNELS_PER_CALL.get(what, 1)
+    launch_counts[what] = launch_counts.get(what, 0) + 1

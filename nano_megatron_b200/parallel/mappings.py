@@ -327,38 +327,49 @@ class ColumnParallelLinear(nn.Module):
         self.buffer_manager = CommunicationBuffer()
         self.sequence_parallel = sequence_parallel
 
-    def forward(self, x: Tensor, *, gelu: bool = False, split_gelu: bool = False):
-        """``split_gelu`` returns ``(pre_activation, gelu(pre_activation))`` so that
-        the following row-parallel linear can fold GELU' into its dgrad GEMM."""
-        if self.sequence_parallel and self.tp_size > 1 and x.dim() == 3 and OF.native_linear_ok(x, self.weight):
+    def forward(self, x: Tensor, *, gelu: bool = False, split_gelu: bool = False, split_act: Optional[str] = None,
+                rope: Any = None):
+        """``split_act`` (``"gelu"`` / ``"swiglu"``; ``split_gelu=True`` means ``"gelu"``)
+        returns ``(pre_activation, act(pre_activation))`` from one GEMM so that
+        the following row-parallel linear can fold the activation's backward
+        into its dgrad GEMM (bf16 GPU path only).  ``rope`` (a
+        :class:`~nano_megatron_b200.ops.gemm.RopeSpec`, bf16 GPU path only)
+        rotates the leading q / k columns of the output in the GEMM epilogue."""
+        if split_gelu and split_act is None:
+            split_act = "gelu"
+        native = OF.native_linear_ok(x, self.weight)
+        if (split_act == "swiglu" or rope is not None) and not native:
+            raise ValueError("the fused SwiGLU / rotary epilogues need bf16 CUDA tensors")
+        want_act = split_act or ("gelu" if gelu else None)
+        if self.sequence_parallel and self.tp_size > 1 and x.dim() == 3 and native:
             from ..ops import fused_tp
             st = fused_tp.tp_fused_for(self.group) if fused_tp.ENABLED else None
             seq_len = x.shape[1] * self.tp_size
             if st is not None and st.supported(x.shape[0] * seq_len, seq_len, self.weight.shape[0]):
                 # all-gather fused into the GEMM (one launch, peers' shards pulled tile by tile)
-                out = fused_tp._SPColumnLinearFn.apply(x, self.weight, self.bias, st, seq_len, self, split_gelu or gelu)
-                if split_gelu:
+                out = fused_tp._SPColumnLinearFn.apply(x, self.weight, self.bias, st, seq_len, self, want_act, rope)
+                if split_act:
                     return out
                 return out[1] if gelu else out
-        if not self.sequence_parallel and self.tp_size > 1 and OF.native_linear_ok(x, self.weight):
+        if not self.sequence_parallel and self.tp_size > 1 and native:
             from ..ops import fused_tp
             st = fused_tp.tp_fused_for(self.group) if fused_tp.ENABLED else None
             rows = x.numel() // x.shape[-1]
             if st is not None and st.all_reduce_supported(rows, x.shape[-1]):
                 # local GEMM; the all-reduce of the input gradient rides in the dgrad GEMM
-                out = fused_tp._TPColumnLinearFn.apply(x, self.weight, self.bias, st, split_gelu or gelu)
-                if split_gelu:
+                out = fused_tp._TPColumnLinearFn.apply(x, self.weight, self.bias, st, want_act, rope)
+                if split_act:
                     return out
                 return out[1] if gelu else out
         if self.sequence_parallel:
             x = gather_from_sequence_parallel_region(x, self.group, self.backend, self.tp_rank, self.tp_size)
         elif self.tp_size > 1:
             x = _CopyToTPRegion.apply(x, self.group, self.backend, self.buffer_manager)
-        if split_gelu:
+        if split_act:
             if OF.native_linear_ok(x, self.weight):
-                return OF.linear_gelu_split(x, self.weight, self.bias)
+                return OF.linear_act_split(x, self.weight, self.bias, split_act)
             return None, OF.linear(x, self.weight, self.bias, gelu=True)
-        return OF.linear(x, self.weight, self.bias, gelu=gelu)
+        return OF.linear(x, self.weight, self.bias, gelu=gelu, rope=rope)
 
 
 class RowParallelLinear(nn.Module):
@@ -379,14 +390,20 @@ class RowParallelLinear(nn.Module):
         if sequence_parallel and self.bias is not None:
             register_sequence_parallel_grad_allreduce(self.bias, group, backend)
 
-    def forward(self, x: Tensor, *, residual: Optional[Tensor] = None, gelu_pre: Optional[Tensor] = None) -> Tensor:
-        """``gelu_pre``: ``x`` is ``gelu(gelu_pre)`` (from ``split_gelu``); the backward
-        then returns the gradient of ``gelu_pre``."""
-        fused = gelu_pre is not None and OF.native_linear_ok(x, self.weight)
+    def forward(self, x: Tensor, *, residual: Optional[Tensor] = None, gelu_pre: Optional[Tensor] = None,
+                act_pre: Optional[Tensor] = None, act: str = "gelu") -> Tensor:
+        """``act_pre``: ``x`` is ``act(act_pre)`` (from ``split_act``; ``gelu_pre`` is
+        the same for ``act="gelu"``); the backward then returns the gradient of
+        ``act_pre``."""
+        if gelu_pre is not None and act_pre is None:
+            act_pre, act = gelu_pre, "gelu"
+        fused = act_pre is not None and OF.native_linear_ok(x, self.weight)
+        if act_pre is not None and not fused:
+            raise ValueError("act_pre needs the bf16 CUDA path")
         if self.tp_size == 1:
             # Nothing to reduce: bias and residual ride in the GEMM epilogue.
             if fused:
-                return OF.linear_from_gelu(gelu_pre, x, self.weight, self.bias, residual)
+                return OF.linear_from_act(act_pre, x, self.weight, self.bias, residual, act)
             return OF.linear(x, self.weight, self.bias, residual=residual)
         if self.sequence_parallel and x.dim() == 3 and OF.native_linear_ok(x, self.weight):
             from ..ops import fused_tp
@@ -394,7 +411,7 @@ class RowParallelLinear(nn.Module):
             if st is not None and st.supported(x.shape[0] * x.shape[1], x.shape[1], self.weight.shape[0]):
                 # GEMM with the reduce-scatter (and bias / residual) fused in
                 return fused_tp._SPRowLinearFn.apply(x, self.weight, self.bias, residual,
-                                                     gelu_pre if fused else None, st, x.shape[1])
+                                                     act_pre if fused else None, st, x.shape[1], act)
         if not self.sequence_parallel and OF.native_linear_ok(x, self.weight):
             from ..ops import fused_tp
             st = fused_tp.tp_fused_for(self.group) if fused_tp.ENABLED else None
@@ -402,8 +419,8 @@ class RowParallelLinear(nn.Module):
             if st is not None and st.all_reduce_supported(rows, self.weight.shape[0]):
                 # GEMM with the all-reduce (and bias / residual) fused in
                 return fused_tp._TPRowLinearFn.apply(x, self.weight, self.bias, residual,
-                                                     gelu_pre if fused else None, st)
-        out = OF.linear_from_gelu(gelu_pre, x, self.weight, None) if fused else OF.linear(x, self.weight, None)
+                                                     act_pre if fused else None, st, act)
+        out = OF.linear_from_act(act_pre, x, self.weight, None, None, act) if fused else OF.linear(x, self.weight, None)
         if self.sequence_parallel:
             out = reduce_scatter_to_sequence_parallel_region(out, self.group, self.backend, self.tp_rank, self.tp_size)
         else:

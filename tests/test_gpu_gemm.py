@@ -111,3 +111,84 @@ def test_gemm_cta_pair_kernel_matches_single_cta_kernel(a_mn, b_mn, m, n, k):
         assert torch.equal(x, y)
     ref = _ref(a, b, a_mn, b_mn) + bias.float() + res.float()
     assert (outs[1][0].float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3
+
+
+def _rel(got, want):
+    return (got.float() - want).norm().item() / (want.norm().item() + 1e-9)
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(64, 4, 4), (128, 2, 1), (96, 3, 1)])
+def test_rope_epilogue_and_its_undo_in_attention_backward(d, hq, hkv):
+    """QKV projection whose epilogue rotates q and k (interleaved pairs, as the
+    reference's apply_rotary_emb) followed by packed attention whose backward
+    un-rotates dq / dk: outputs and all gradients against fp32 autograd through
+    projection -> rotation -> causal attention."""
+    from nano_megatron_b200.ops import functional as OF
+    from nano_megatron_b200.ops.attention import flash_attention_packed
+    from nano_megatron_b200.ops.gemm import RopeSpec
+    from nano_megatron_b200.reference.layers import apply_rotary_emb, precompute_freqs_cis
+
+    torch.manual_seed(5)
+    b, s, h = 2, 256, 192
+    n = (hq + 2 * hkv) * d
+    x = _rand((b, s, h), 0.5).requires_grad_(True)
+    w = _rand((n, h), 0.08).requires_grad_(True)
+    bias = _rand((n,), 0.1).requires_grad_(True)
+    positions = torch.arange(s, device="cuda").unsqueeze(0).expand(b, -1).contiguous()
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, d, 2, device="cuda").float() / d))
+    spec = RopeSpec(RopeSpec.make_table(inv_freq, s), positions, (hq + hkv) * d)
+    scale = d ** -0.5
+    qkv = OF.linear(x, w, bias, rope=spec)
+    out = flash_attention_packed(qkv, hq, hkv, d, scale, rope=spec)
+    g = _rand(out.shape, 1.0)
+    out.backward(g)
+
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, bias))
+    y = xf @ wf.t() + bf
+    q = y[..., : hq * d].view(b, s, hq, d).transpose(1, 2)
+    k = y[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d).transpose(1, 2)
+    v = y[..., (hq + hkv) * d:].view(b, s, hkv, d).transpose(1, 2)
+    ang = precompute_freqs_cis(d, s).to("cuda")[positions]
+    q, k = apply_rotary_emb(q, ang), apply_rotary_emb(k, ang)
+    # the rotated projection output itself
+    want_qkv = torch.cat([q.transpose(1, 2).reshape(b, s, -1), k.transpose(1, 2).reshape(b, s, -1),
+                          y[..., (hq + hkv) * d:]], dim=-1)
+    assert _rel(qkv, want_qkv.detach()) < 1e-2
+    rep = hq // hkv
+    k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+    ref = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale).transpose(1, 2)
+    assert _rel(out, ref.detach()) < 2e-2
+    ref.backward(g.float())
+    assert _rel(x.grad, xf.grad) < 3e-2
+    assert _rel(w.grad, wf.grad) < 3e-2
+    assert _rel(bias.grad, bf.grad) < 3e-2
+
+
+@pytest.mark.parametrize("m,f,k,with_bias", [(512, 256, 128, True), (384, 160, 192, False), (4096, 2048, 1024, False)])
+def test_swiglu_epilogues(m, f, k, with_bias):
+    """fc1 with silu(gate) * up in its epilogue and fc2 whose dgrad epilogue
+    applies the SwiGLU backward, against fp32 autograd."""
+    from nano_megatron_b200.ops import functional as OF
+
+    torch.manual_seed(6)
+    h = 256
+    x = _rand((m, k), 0.5).requires_grad_(True)
+    w1 = _rand((2 * f, k), 0.1).requires_grad_(True)
+    b1 = _rand((2 * f,), 0.2).requires_grad_(True) if with_bias else None
+    w2 = _rand((h, f), 0.1).requires_grad_(True)
+    pre, act = OF.linear_act_split(x, w1, b1, "swiglu")
+    y = OF.linear_from_act(pre, act, w2, None, None, "swiglu")
+    g = _rand(y.shape, 1.0)
+    y.backward(g)
+
+    xf, w1f, w2f = (t.detach().float().requires_grad_(True) for t in (x, w1, w2))
+    b1f = b1.detach().float().requires_grad_(True) if with_bias else None
+    pf = xf @ w1f.t() + (b1f if with_bias else 0.0)
+    af = torch.nn.functional.silu(pf[:, :f]) * pf[:, f:]
+    yf = af @ w2f.t()
+    assert _rel(pre, pf.detach()) < 1e-2 and _rel(act, af.detach()) < 1.5e-2 and _rel(y, yf.detach()) < 2e-2
+    yf.backward(g.float())
+    assert _rel(x.grad, xf.grad) < 3e-2
+    assert _rel(w1.grad, w1f.grad) < 3e-2 and _rel(w2.grad, w2f.grad) < 3e-2
+    if with_bias:
+        assert _rel(b1.grad, b1f.grad) < 3e-2

@@ -47,11 +47,17 @@ def test_bf16_model_tracks_fp32_oracle(ctx, name):
                 p.mul_(0.5)
     model = build_tp_gpt_from_reference(ref, ctx).to("cuda", dtype=torch.bfloat16)
     ids = torch.randint(0, cfg.vocab_size, (2, 256))
+    before = dict(native.launch_counts)
     logits = model(ids.cuda())
     loss = model.shifted_cross_entropy(logits, ids.cuda())
     loss.backward()
     torch.cuda.synchronize()
     native.check_status()
+    if name == "rope_swiglu_gqa":
+        # rotary embedding and SwiGLU ride in GEMM epilogues (and the attention backward's last
+        # kernel): no stand-alone rotation or activation kernel ran, forward or backward
+        for entry in ("nmb_rope", "nmb_swiglu_fwd", "nmb_swiglu_bwd"):
+            assert native.launch_counts.get(entry, 0) == before.get(entry, 0), entry
     cfg_cpu = ReferenceGPTConfig(**{**cfg.__dict__, "attn_backend": "unfused"})
     ref.config = cfg_cpu
     for blk in ref.blocks:
