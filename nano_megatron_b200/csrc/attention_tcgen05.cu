@@ -1085,9 +1085,10 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   e = cudaGetLastError();
   if (e != cudaSuccess) return 400 + e;
   {
-    // un-rotating dk in place needs the whole key sequence in one local chunk of the query's length
+    // dk is un-rotated in place when the whole key sequence is one local chunk of the
+    // query's length; with several chunks (context parallelism) dk still has to be
+    // summed over ranks, and the kernel that sums it un-rotates it
     const bool unrope_k = rope_table != nullptr && n_chunks == 1 && chunk_len == Sq;
-    if (rope_table != nullptr && !unrope_k) return kBadArgument;
     long long octets = static_cast<long long>(B) * Sq * Hq * d / 8;
     if (unrope_k) octets += static_cast<long long>(B) * Sq * Hkv * d / 8;
     const int threads = 256;

@@ -267,6 +267,64 @@ __global__ void embedding_scatter_kernel(const long long* __restrict__ ids, cons
   }
 }
 
+// Context-parallel attention backward, owner side: dK and dV of this rank's
+// key/value shard are the sums of the contributions of every rank that can see
+// the shard (ranks `first` .. n-1; each stored its tiles into slot [its rank] of
+// this rank's staging buffers from inside its attention-backward kernel).  One
+// launch: blocks of equal index on all ranks meet in a flag round (a rank gets
+// here only after its attention backward has finished, so all contributions
+// have been stored), then every block sums its share of the slots in fp32, in
+// slot order, and writes bf16 results to the (strided) gradient tensors.  With a
+// rotary table dK is un-rotated on the way out.  This replaces the reference's
+// reduce-scatter of the gathered dK / dV
+// (nano_megatron/parallel/context_parallel.py:175-181).
+__device__ __forceinline__ void unrope8_bf(float (&x)[8], const float2* table, long long pos, int half, int pair0) {
+  const float4* tp = reinterpret_cast<const float4*>(table + pos * half + pair0);
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const float4 cs = __ldg(tp + q);
+    const float a0 = x[4 * q], a1 = x[4 * q + 1], b0 = x[4 * q + 2], b1 = x[4 * q + 3];
+    x[4 * q] = a0 * cs.x + a1 * cs.y;
+    x[4 * q + 1] = -a0 * cs.y + a1 * cs.x;
+    x[4 * q + 2] = b0 * cs.z + b1 * cs.w;
+    x[4 * q + 3] = -b0 * cs.w + b1 * cs.z;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+cp_dkv_reduce_kernel(const __nv_bfloat16* __restrict__ stage_k, const __nv_bfloat16* __restrict__ stage_v,
+                     __nv_bfloat16* __restrict__ out_k, __nv_bfloat16* __restrict__ out_v, long long out_sb,
+                     long long out_ss, long long out_sh, int B, int S, int H, int d, int first, PeerPtrs pads,
+                     uint32_t* epochs, int channel, int rank, int n, const float2* __restrict__ rope_table,
+                     const long long* __restrict__ rope_pos, int* status, long long budget) {
+  __shared__ uint32_t epoch_s;
+  uint32_t* my_epoch = epochs + channel * kMaxBlocks + blockIdx.x;
+  if (threadIdx.x == 0) epoch_s = *my_epoch;
+  __syncthreads();
+  const bool ok = block_barrier(pads, channel, rank, n, epoch_s + 1, status, budget, 67);
+  if (threadIdx.x == 0) *my_epoch = epoch_s + 1;
+  if (!ok) return;
+  const int per_row = d / 8;
+  const long long slot_vecs = static_cast<long long>(B) * S * H * per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < 2 * slot_vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const bool is_v = i >= slot_vecs;
+    const long long j = is_v ? i - slot_vecs : i;
+    const uint4* stage = reinterpret_cast<const uint4*>(is_v ? stage_v : stage_k);
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int slot = first; slot < n; ++slot) Vec16<__nv_bfloat16>::add(acc, stage[slot * slot_vecs + j]);
+    const int c8 = static_cast<int>(j % per_row);
+    const long long row = j / per_row;  // (b * S + s) * H + h
+    const int h = row % H;
+    const long long bs = row / H;
+    if (!is_v && rope_table != nullptr) unrope8_bf(acc, rope_table, rope_pos[bs], d / 2, c8 * 4);
+    __nv_bfloat16* dst = (is_v ? out_v : out_k) + (bs / S) * out_sb + (bs % S) * out_ss + h * out_sh + c8 * 8;
+    *reinterpret_cast<uint4*>(dst) = Vec16<__nv_bfloat16>::pack(acc, 1.f);
+  }
+}
+
 // Stand-alone barrier (one block), e.g. "my buffer is published" between kernels.
 __global__ void barrier_kernel(PeerPtrs pads, uint32_t* epochs, int channel, int rank, int n, int* status,
                                long long budget) {
@@ -445,6 +503,33 @@ extern "C" int nmb_symm_barrier(void* const* pads, void* epochs, int channel, in
   fill(p, pads, n);
   barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, static_cast<uint32_t*>(epochs), channel, rank, n,
                                                                   status, budget_cycles);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+// stage_k / stage_v: this rank's [n][B, S, H, d] staging buffers; out_k / out_v:
+// [B, S, H, d] views with element strides (out_sb, out_ss, out_sh), 16-byte
+// aligned rows.  All ranks of the group launch it with the same shapes.
+extern "C" int nmb_cp_dkv_reduce(const void* stage_k, const void* stage_v, void* out_k, void* out_v, long long out_sb,
+                                 long long out_ss, long long out_sh, int B, int S, int H, int d, int first,
+                                 void* const* pads, void* epochs, int channel, int rank, int n,
+                                 const void* rope_table, const long long* rope_pos, int* status,
+                                 long long budget_cycles, void* stream) {
+  if (n < 1 || n > kMaxRanks || channel < 0 || channel >= kChannels || d % 8 != 0 || first < 0 || first >= n)
+    return kBadArgument;
+  if ((out_sb | out_ss | out_sh) % 8 != 0) return kBadArgument;
+  PeerPtrs p;
+  fill(p, pads, n);
+  const long long vecs = 2LL * B * S * H * (d / 8);
+  int blocks = static_cast<int>((vecs + 1023) / 1024);
+  if (blocks < 1) blocks = 1;
+  if (blocks > 2 * 148) blocks = 2 * 148;
+  if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  cp_dkv_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(stage_k), static_cast<const __nv_bfloat16*>(stage_v),
+      static_cast<__nv_bfloat16*>(out_k), static_cast<__nv_bfloat16*>(out_v), out_sb, out_ss, out_sh, B, S, H, d, first,
+      p, static_cast<uint32_t*>(epochs), channel, rank, n, static_cast<const float2*>(rope_table), rope_pos, status,
+      budget_cycles);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + e;
 }

@@ -169,6 +169,38 @@ class SymmetricWorkspace:
             arr[i] = p
         return arr
 
+    def contains(self, t: torch.Tensor) -> bool:
+        """Whether ``t`` lives in symmetric memory of this workspace."""
+        ptr = t.data_ptr()
+        return any(a.local_ptr <= ptr < a.local_ptr + a.nbytes for a in self._allocs)
+
+    def peer_strided(self, t: torch.Tensor, rank: int) -> torch.Tensor:
+        """``t`` (any strided view into symmetric memory) as seen in ``rank``'s
+        copy of the same allocation: same shape and strides, peer-mapped memory."""
+        if rank == self.rank:
+            return t
+        ptr = self.peers_of(t)[rank]
+        span = sum((n - 1) * st for n, st in zip(t.shape, t.stride())) + 1
+        raw = torch.as_tensor(_RawCuda(ptr, span * t.element_size()), device=self.device)
+        return raw.view(t.dtype).as_strided(t.shape, t.stride())
+
+    def cp_dkv_reduce(self, stage_k: torch.Tensor, stage_v: torch.Tensor, out_k: torch.Tensor, out_v: torch.Tensor,
+                      first: int, *, channel: int = CHANNEL_CP, rope=None) -> None:
+        """``out_k / out_v [B, S, H, d] = sum over slots first.. of stage_k / stage_v
+        [size, B, S, H, d]`` after a flag round of the group inside the same
+        launch (see ``cp_dkv_reduce_kernel``); ``rope`` un-rotates dK."""
+        b, s, h, d = out_k.shape
+        assert out_k.stride() == out_v.stride() and out_k.stride(3) == 1
+        rc = native.lib().nmb_cp_dkv_reduce(
+            native.ptr(stage_k), native.ptr(stage_v), native.ptr(out_k), native.ptr(out_v),
+            ctypes.c_longlong(out_k.stride(0)), ctypes.c_longlong(out_k.stride(1)), ctypes.c_longlong(out_k.stride(2)),
+            ctypes.c_int(b), ctypes.c_int(s), ctypes.c_int(h), ctypes.c_int(d), ctypes.c_int(first),
+            self.pad.table(), native.ptr(self.epochs), ctypes.c_int(channel), ctypes.c_int(self.rank),
+            ctypes.c_int(self.size), native.ptr(rope.table if rope is not None else None),
+            native.ptr(rope.positions if rope is not None else None), native.ptr(self.status),
+            ctypes.c_longlong(self.budget), native.stream_ptr(self.device))
+        native.check_rc(rc, "nmb_cp_dkv_reduce")
+
     def peer_view(self, t: torch.Tensor, rank: int) -> torch.Tensor:
         """``t``'s counterpart on ``rank`` as a tensor of this process (peer-mapped memory)."""
         if rank == self.rank:

@@ -47,17 +47,41 @@ class _KVExchange:
         self.cursor += 1
         return index, pair
 
+    def next_packed(self, like: Tensor, lease: bool) -> tuple[int, Tensor]:
+        """Like ``next_slot`` for ONE buffer of ``like``'s shape (a packed QKV output)."""
+        while self.cursor < len(self.slots) and self.leased[self.cursor]:
+            self.cursor += 1
+        if self.cursor == len(self.slots):
+            buf = self.ws.alloc_tensor(like.numel(), like.dtype).view(like.shape)
+            self.slots.append((buf, buf))
+            self.leased.append(False)
+        index = self.cursor
+        buf = self.slots[index][0]
+        if buf.shape != like.shape:
+            raise RuntimeError("context-parallel QKV shape changed between steps")
+        self.leased[index] = lease
+        self.cursor += 1
+        return index, buf
+
     def release(self, index: int) -> None:
         self.leased[index] = False
 
     def stage(self, like: Tensor) -> tuple[Tensor, Tensor]:
+        """dK / dV staging ``[size, *like.shape]``, two pairs used alternately: a
+        rank may already store the next layer's tiles into a peer's staging while
+        that peer still sums the previous layer's."""
         key = (tuple(like.shape), like.dtype)
         if key not in self.staging:
             n = self.ws.size * like.numel()
-            dk = self.ws.alloc_tensor(n, like.dtype).view(self.ws.size, *like.shape)
-            dv = self.ws.alloc_tensor(n, like.dtype).view(self.ws.size, *like.shape)
-            self.staging[key] = (dk, dv)
-        return self.staging[key]
+            pairs = []
+            for _ in range(2):
+                dk = self.ws.alloc_tensor(n, like.dtype).view(self.ws.size, *like.shape)
+                dv = self.ws.alloc_tensor(n, like.dtype).view(self.ws.size, *like.shape)
+                pairs.append((dk, dv))
+            self.staging[key] = [pairs, 0]
+        pairs, turn = self.staging[key]
+        self.staging[key][1] = turn ^ 1
+        return pairs[turn]
 
 
 class _SlotLease:
@@ -92,34 +116,44 @@ def begin_step(ws: SymmetricWorkspace) -> None:
 class _CPFlashPeer(torch.autograd.Function):
     """Context-parallel attention whose kernel reads the peers' K/V in place.
 
-    forward : publish K/V in this rank's symmetric slot, barrier, then ONE
-              attention launch whose TMA loads fetch chunk c from rank c's slot.
-    backward: ONE launch computes dQ and this rank's dK/dV contribution to every
-              visible chunk, storing chunk c's tiles straight into slot
-              [my_rank] of rank c's staging buffer; after a barrier each rank
-              sums the slots of the ranks that can see it (rank >= own).
+    forward : K/V must be peer-addressable.  When the projection wrote them
+              straight into symmetric memory (``qkv_slot``) they are used where
+              they are; otherwise they are copied into a leased slot.  One
+              barrier (every rank's K/V is published), then ONE attention launch
+              whose TMA loads fetch chunk c from rank c's memory.
+    backward: ONE attention launch computes dQ and this rank's dK/dV contribution
+              to every visible chunk, storing chunk c's tiles straight into slot
+              [my_rank] of rank c's staging buffer; then ONE launch on every rank
+              meets the group in a flag round and sums the slots of the ranks
+              that can see this rank's shard (rank >= own), un-rotating dK when
+              the projection applied rotary embeddings.
     """
 
     @staticmethod
     def forward(ctx: Any, q: Tensor, k: Tensor, v: Tensor, scale: float, ws: SymmetricWorkspace, cp_rank: int,
-                cp_size: int):
+                cp_size: int, lease: Any = None, rope: Any = None):
         from ..ops.attention import attn_fwd
 
         ex = _exchange(ws)
-        # Inside a CUDA graph capture forward and backward of the step are recorded
-        # together and replayed as a unit: nothing stays outstanding, no lease.
-        lease = any(ctx.needs_input_grad[:3]) and not torch.cuda.is_current_stream_capturing()
-        index, (k_slot, v_slot) = ex.next_slot(k, lease=lease)
-        ctx.lease = _SlotLease(ex, index) if lease else None
-        k_slot.copy_(k)
-        v_slot.copy_(v)
+        if ws.contains(k) and ws.contains(v):
+            k_slot, v_slot = k, v                    # already in symmetric memory (leased by the caller)
+        else:
+            # Inside a CUDA graph capture forward and backward of the step are recorded
+            # together and replayed as a unit: nothing stays outstanding, no lease.
+            take = any(ctx.needs_input_grad[:3]) and not torch.cuda.is_current_stream_capturing()
+            k, v = k.contiguous(), v.contiguous()
+            index, (k_slot, v_slot) = ex.next_slot(k, lease=take)
+            lease = _SlotLease(ex, index) if take else None
+            k_slot.copy_(k)
+            v_slot.copy_(v)
+        ctx.lease = lease
         ws.barrier(CHANNEL_CP)                       # every rank's K/V is published
-        ks = [ws.peer_view(k_slot, r) for r in range(cp_size)]
-        vs = [ws.peer_view(v_slot, r) for r in range(cp_size)]
+        ks = [ws.peer_strided(k_slot, r) for r in range(cp_size)]
+        vs = [ws.peer_strided(v_slot, r) for r in range(cp_size)]
         out, lse = attn_fwd(q, ks, vs, scale, q_pos0=cp_rank * q.shape[1])
         ctx.save_for_backward(q, out, lse)
         ctx.kv = (k_slot, v_slot)
-        ctx.meta = (scale, ws, cp_rank, cp_size)
+        ctx.meta = (scale, ws, cp_rank, cp_size, rope)
         return out
 
     @staticmethod
@@ -128,28 +162,46 @@ class _CPFlashPeer(torch.autograd.Function):
 
         q, out, lse = ctx.saved_tensors
         k_slot, v_slot = ctx.kv
-        scale, ws, cp_rank, cp_size = ctx.meta
+        scale, ws, cp_rank, cp_size, rope = ctx.meta
         ex = _exchange(ws)
-        dk_stage, dv_stage = ex.stage(k_slot)
-        ks = [ws.peer_view(k_slot, r) for r in range(cp_size)]
-        vs = [ws.peer_view(v_slot, r) for r in range(cp_size)]
+        like = torch.empty(k_slot.shape, dtype=k_slot.dtype, device="meta")
+        dk_stage, dv_stage = ex.stage(like)
+        ks = [ws.peer_strided(k_slot, r) for r in range(cp_size)]
+        vs = [ws.peer_strided(v_slot, r) for r in range(cp_size)]
         # chunk c's gradient tiles go to slot [cp_rank] of rank c's staging buffer
         dks = [ws.peer_view(dk_stage, r)[cp_rank] for r in range(cp_size)]
         dvs = [ws.peer_view(dv_stage, r)[cp_rank] for r in range(cp_size)]
-        ws.barrier(CHANNEL_CP)                       # the staging area is free (previous layer consumed it)
-        dq, _, _ = attn_bwd(q, ks, vs, out, dout, lse, scale, q_pos0=cp_rank * q.shape[1], dk_chunks=dks,
-                            dv_chunks=dvs)
-        ws.barrier(CHANNEL_CP)                       # all contributions have landed
-        dk = dk_stage[cp_rank:].float().sum(0).to(k_slot.dtype)
-        dv = dv_stage[cp_rank:].float().sum(0).to(v_slot.dtype)
+        # dq, dk and dv are slices of ONE packed gradient, as the projection's backward wants it
+        b, s, hq, d = q.shape
+        hkv = k_slot.shape[2]
+        dqkv = torch.empty((b, s, (hq + 2 * hkv) * d), dtype=q.dtype, device=q.device)
+        dq = dqkv[..., : hq * d].view(b, s, hq, d)
+        dk = dqkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+        dv = dqkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
+        attn_bwd(q, ks, vs, out, dout, lse, scale, q_pos0=cp_rank * s, dk_chunks=dks, dv_chunks=dvs, dq=dq, rope=rope)
+        # flag round + sum of the contributions (+ inverse rotation of dK) in one launch
+        ws.cp_dkv_reduce(dk_stage, dv_stage, dk, dv, cp_rank, rope=rope)
         if ctx.lease is not None:
             ctx.lease.release()
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 def cp_flash_attention_peer(q: Tensor, k: Tensor, v: Tensor, scale: float, ws: SymmetricWorkspace, cp_rank: int,
-                            cp_size: int) -> Tensor:
-    return _CPFlashPeer.apply(q, k.contiguous(), v.contiguous(), float(scale), ws, cp_rank, cp_size)
+                            cp_size: int, lease: Any = None, rope: Any = None) -> Tensor:
+    """``rope``: q and k were rotated by the projection's epilogue; the backward
+    returns un-rotated dq / dk (see ``flash_attention_packed``)."""
+    return _CPFlashPeer.apply(q, k, v, float(scale), ws, cp_rank, cp_size, lease, rope)
+
+
+def lease_packed_slot(ws: SymmetricWorkspace, shape: tuple, dtype: torch.dtype, will_backward: bool):
+    """A symmetric buffer for a packed QKV projection output (the K and V slices
+    of it are what the peers read), leased until the attention's backward has
+    run.  Returns ``(buffer, lease or None)``."""
+    ex = _exchange(ws)
+    take = will_backward and not torch.cuda.is_current_stream_capturing()
+    like = torch.empty(shape, dtype=dtype, device="meta")
+    index, buf = ex.next_packed(like, lease=take)
+    return buf, (_SlotLease(ex, index) if take else None)
 
 
 class _SPEmbeddingFn(torch.autograd.Function):

@@ -196,6 +196,24 @@ class TPCausalSelfAttention(nn.Module):
                 b, s, _ = qkv.shape
                 context = flash_attention_packed(qkv.contiguous(), hq, hkv, d, self.scale, rope=spec)
                 return self.out_proj(context.view(b, s, hq * d), residual=residual)
+            if self._cp_size > 1 and self.qkv_proj.tp_size == 1 and x.dim() == 3 and \
+                    (not rotate or (d % 32 == 0 and self.config.rotary_dim == d)):
+                from ..distributed import symmetric
+                ws = symmetric.workspace_for(self._cp_group)
+                if ws is not None and x.shape[1] % 128 == 0:
+                    # The projection writes q | k | v into symmetric memory: the peers' attention
+                    # kernels read K and V from there in place (no copy into an exchange buffer),
+                    # rotary embedding rides in the epilogue and is undone inside the backward.
+                    from ..distributed.symm_ops import cp_flash_attention_peer, lease_packed_slot
+                    b, s = x.shape[0], x.shape[1]
+                    buf, lease = lease_packed_slot(ws, (b, s, (hq + 2 * hkv) * d), x.dtype,
+                                                   torch.is_grad_enabled() and x.requires_grad)
+                    spec = self._rope_spec(x.device, positions, (hq + hkv) * d) if rotate else None
+                    qkv = self.qkv_proj(x, rope=spec, out=buf)
+                    q, k, v = split_packed_qkv(qkv, hq, hkv, d)
+                    context = cp_flash_attention_peer(q, k, v, self.scale, ws, self._cp_rank, self._cp_size,
+                                                      lease, spec)
+                    return self.out_proj(context.view(b, s, hq * d), residual=residual)
             qkv = self.qkv_proj(x)
             b, s, _ = qkv.shape
             if self._cp_size == 1 and not rotate and qkv.is_contiguous():

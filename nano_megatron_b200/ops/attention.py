@@ -176,6 +176,14 @@ class _SplitPacked(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dq, dk, dv):
         b, s = dq.shape[0], dq.shape[1]
+        hq, hkv, d = ctx.meta
+        width = (hq + 2 * hkv) * d
+        packed = (dq.stride() == (s * width, width, d, 1) and dk.stride() == dq.stride() and dv.stride() == dq.stride()
+                  and dk.data_ptr() == dq.data_ptr() + 2 * hq * d and dv.data_ptr() == dk.data_ptr() + 2 * hkv * d
+                  and dq.dtype == torch.bfloat16)
+        if packed:
+            # the three gradients already are the slices of one packed buffer: hand that buffer back
+            return dq.as_strided((b, s, width), (s * width, width, 1)), None, None, None
         return torch.cat([dq.reshape(b, s, -1), dk.reshape(b, s, -1), dv.reshape(b, s, -1)], dim=-1), None, None, None
 
 

@@ -55,7 +55,7 @@ class _LinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x: Tensor, weight: Tensor, bias: Optional[Tensor], residual: Optional[Tensor], gelu: bool,
-                rope: Optional[RopeSpec] = None):
+                rope: Optional[RopeSpec] = None, out: Optional[Tensor] = None):
         x2 = x.reshape(-1, x.shape[-1])
         if x2.stride(-1) != 1 or (x2.stride(0) % 8) != 0:
             x2 = x2.contiguous()
@@ -69,9 +69,12 @@ class _LinearFn(torch.autograd.Function):
             # q and k heads leave the projection already rotated; the attention
             # backward hands back the gradient of the un-rotated output, so the
             # backward below is the plain linear one
-            y = gemm_bf16(x2, weight, bias=bias, mode=EPI_ROPE, rope=rope)
+            y = gemm_bf16(x2, weight, bias=bias, mode=EPI_ROPE, rope=rope,
+                          out=out.view(-1, n) if out is not None else None)
         else:
-            y = gemm_bf16(x2, weight, bias=bias, residual=res2, mode=EPI_PLAIN)
+            # ``out``: a caller-provided destination (e.g. symmetric memory that peers read)
+            y = gemm_bf16(x2, weight, bias=bias, residual=res2, mode=EPI_PLAIN,
+                          out=out.view(-1, n) if out is not None else None)
         ctx.save_for_backward(x2, weight, pre)
         ctx.has_bias = bias is not None
         ctx.has_res = residual is not None
@@ -101,7 +104,7 @@ class _LinearFn(torch.autograd.Function):
         db = None
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = _deliver_grad(b_param, lambda out, acc: kernels.col_sum(dz, out=out, accumulate=acc))
-        return dx, dw, db, d_res, None, None
+        return dx, dw, db, d_res, None, None, None
 
 
 def _rows(t: Tensor, width: int) -> Tensor:
@@ -216,13 +219,13 @@ def native_linear_ok(x: Tensor, weight: Tensor) -> bool:
 
 
 def linear(x: Tensor, weight: Tensor, bias: Optional[Tensor] = None, *, residual: Optional[Tensor] = None,
-           gelu: bool = False, rope: Optional[RopeSpec] = None) -> Tensor:
+           gelu: bool = False, rope: Optional[RopeSpec] = None, out: Optional[Tensor] = None) -> Tensor:
     """``act(x @ weight.T + bias) + residual`` (``gelu`` and ``residual`` are exclusive).
     ``rope`` (native path only) rotates the leading q / k columns in the epilogue."""
     assert not (gelu and residual is not None)
     if native_linear_ok(x, weight):
-        return _LinearFn.apply(x, weight, bias, residual, gelu, rope)
-    assert rope is None, "the rotary epilogue exists on the native path only"
+        return _LinearFn.apply(x, weight, bias, residual, gelu, rope, out)
+    assert rope is None and out is None, "the rotary epilogue / output buffer exist on the native path only"
     # Rows that are not multiples of 16 bytes cannot be described to TMA; such
     # (toy) shapes use the PyTorch expression below.
     y = F.linear(x, weight, bias)

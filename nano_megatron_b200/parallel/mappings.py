@@ -328,13 +328,17 @@ class ColumnParallelLinear(nn.Module):
         self.sequence_parallel = sequence_parallel
 
     def forward(self, x: Tensor, *, gelu: bool = False, split_gelu: bool = False, split_act: Optional[str] = None,
-                rope: Any = None):
+                rope: Any = None, out: Optional[Tensor] = None):
         """``split_act`` (``"gelu"`` / ``"swiglu"``; ``split_gelu=True`` means ``"gelu"``)
         returns ``(pre_activation, act(pre_activation))`` from one GEMM so that
         the following row-parallel linear can fold the activation's backward
         into its dgrad GEMM (bf16 GPU path only).  ``rope`` (a
         :class:`~nano_megatron_b200.ops.gemm.RopeSpec`, bf16 GPU path only)
-        rotates the leading q / k columns of the output in the GEMM epilogue."""
+        rotates the leading q / k columns of the output in the GEMM epilogue.
+        ``out`` (``tp_size == 1``, bf16 GPU path) is the tensor the GEMM writes
+        its result into, e.g. symmetric memory that other ranks read in place."""
+        if out is not None and (self.tp_size > 1 or split_act or gelu):
+            raise ValueError("an output buffer is supported for a plain projection at tp_size == 1")
         if split_gelu and split_act is None:
             split_act = "gelu"
         native = OF.native_linear_ok(x, self.weight)
@@ -369,7 +373,7 @@ class ColumnParallelLinear(nn.Module):
             if OF.native_linear_ok(x, self.weight):
                 return OF.linear_act_split(x, self.weight, self.bias, split_act)
             return None, OF.linear(x, self.weight, self.bias, gelu=True)
-        return OF.linear(x, self.weight, self.bias, gelu=gelu, rope=rope)
+        return OF.linear(x, self.weight, self.bias, gelu=gelu, rope=rope, out=out)
 
 
 class RowParallelLinear(nn.Module):
