@@ -199,6 +199,116 @@ allreduce_scale_light_kernel(const __grid_constant__ PeerPtrs bufs, const __grid
   allreduce_scale_body<T, 4>(bufs, pads, epochs, channel, rank, n, n_vec, scale, status, budget);
 }
 
+// ---------------------------------------------------------------------------
+// In-switch all-reduce (NVLS): the buffer is mapped at the same offset of a
+// multicast address on every rank.  `multimem.ld_reduce` on that address makes
+// the NVSwitch read the element from all ranks and return the sum (accumulated
+// in fp32), `multimem.st` writes a value to all ranks at once.  Block b owns the
+// b-th slice of the buffer, inside it rank r reduces and broadcasts the r-th
+// sub-slice: every element crosses this GPU's links once in and once out,
+// instead of (n-1)/n of the buffer twice with peer loads, and a thread issues
+// one load and one store per 16 bytes whatever the number of ranks.  The flag
+// rounds before and after are the plain peer-memory ones (`block_barrier`).
+// This is multicast *addressing* for reductions; no TMA or bulk load with
+// cluster multicast is involved.
+template <typename T>
+struct Multimem;
+template <>
+struct Multimem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ uint4 scale(const uint4& v, float s) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = unpack_bf16x2(w[k]);
+      o[k] = pack_bf16x2(f.x * s, f.y * s);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+  }
+};
+template <>
+struct Multimem<float> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ uint4 scale(const uint4& v, float s) {
+    return make_uint4(__float_as_uint(__uint_as_float(v.x) * s), __float_as_uint(__uint_as_float(v.y) * s),
+                      __float_as_uint(__uint_as_float(v.z) * s), __float_as_uint(__uint_as_float(v.w) * s));
+  }
+};
+__device__ __forceinline__ void multimem_st(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+template <typename T, int U>
+__device__ __forceinline__ void multimem_allreduce_body(uint8_t* mc, const PeerPtrs& pads, uint32_t* epochs, int channel,
+                                                        int rank, int n, long long n_vec, float scale, int* status,
+                                                        long long budget) {
+  __shared__ uint32_t epoch_s;
+  uint32_t* my_epoch = epochs + channel * kMaxBlocks + blockIdx.x;
+  if (threadIdx.x == 0) epoch_s = *my_epoch;
+  __syncthreads();
+  const uint32_t e0 = epoch_s;
+  const long long per_block = (n_vec + gridDim.x - 1) / gridDim.x;
+  const long long blk_lo = per_block * blockIdx.x;
+  long long blk_hi = blk_lo + per_block;
+  if (blk_hi > n_vec) blk_hi = n_vec;
+  const long long blk_len = blk_hi > blk_lo ? blk_hi - blk_lo : 0;
+  const long long per_rank = (blk_len + n - 1) / n;
+  bool ok = block_barrier(pads, channel, rank, n, e0 + 1, status, budget, 71);  // every rank's input is ready
+  if (ok) {
+    const long long lo = blk_lo + per_rank * rank;
+    long long hi = lo + per_rank;
+    if (hi > blk_hi) hi = blk_hi;
+    for (long long base = lo + threadIdx.x; base < hi; base += static_cast<long long>(blockDim.x) * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + static_cast<long long>(u) * blockDim.x;
+        if (i < hi) v[u] = Multimem<T>::ld_reduce(mc + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + static_cast<long long>(u) * blockDim.x;
+        if (i < hi) multimem_st(mc + i * 16, Multimem<T>::scale(v[u], scale));
+      }
+    }
+  }
+  // every rank's sub-slice has been written everywhere (and nobody still reads the inputs)
+  block_barrier(pads, channel, rank, n, e0 + 2, status, budget, 72);
+  if (threadIdx.x == 0) *my_epoch = e0 + 2;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+multimem_allreduce_kernel(uint8_t* mc, const __grid_constant__ PeerPtrs pads, uint32_t* epochs, int channel, int rank,
+                          int n, long long n_vec, float scale, int* status, long long budget) {
+  multimem_allreduce_body<T, 4>(mc, pads, epochs, channel, rank, n, n_vec, scale, status, budget);
+}
+
+// Overlap-first variant (see allreduce_scale_light_kernel for the sizing).
+template <typename T>
+__global__ void __maxnreg__(80)
+multimem_allreduce_light_kernel(uint8_t* mc, const __grid_constant__ PeerPtrs pads, uint32_t* epochs, int channel,
+                                int rank, int n, long long n_vec, float scale, int* status, long long budget) {
+  multimem_allreduce_body<T, 4>(mc, pads, epochs, channel, rank, n, n_vec, scale, status, budget);
+}
+
 // All-gather through peer stores: every rank writes its `n_vec` 16-byte vectors
 // into slot [rank] of every rank's `[n][n_vec]` destination, then the blocks of
 // equal index meet in a barrier.  Small-message replacement for NCCL
@@ -419,6 +529,12 @@ extern "C" int nmb_comm_configure() {
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(allreduce_scale_light_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(multimem_allreduce_light_kernel<__nv_bfloat16>,
+                             cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(multimem_allreduce_light_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
   return e == cudaSuccess ? 0 : 300 + e;
 }
 
@@ -459,6 +575,37 @@ extern "C" int nmb_allreduce_scale(void* const* bufs, void* const* pads, void* e
   else
     allreduce_scale_kernel<float><<<blocks, 512, 0, s>>>(b, p, static_cast<uint32_t*>(epochs), channel, rank, n,
                                                          numel / per, scale, status, budget_cycles);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + e;
+}
+
+// In-place all-reduce (sum) * scale through the multicast mapping `mc` of a
+// buffer of `numel` elements (same layout rules as nmb_allreduce_scale).
+extern "C" int nmb_multimem_allreduce_scale(void* mc, void* const* pads, void* epochs, int channel, int rank, int n,
+                                            long long numel, int is_bf16, float scale, int blocks, int* status,
+                                            long long budget_cycles, void* stream) {
+  if (mc == nullptr || n < 2 || n > kMaxRanks || channel < 0 || channel >= kChannels) return kBadArgument;
+  if (reinterpret_cast<uintptr_t>(mc) & 15) return kBadArgument;
+  const int per = is_bf16 ? 8 : 4;
+  if (numel % per != 0) return kBadArgument;
+  const bool light = blocks < 0;
+  if (light) blocks = -blocks;
+  if (blocks < 1) blocks = 1;
+  if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  PeerPtrs p;
+  fill(p, pads, n);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* m = static_cast<uint8_t*>(mc);
+  uint32_t* ep = static_cast<uint32_t*>(epochs);
+  const long long n_vec = numel / per;
+  if (light && is_bf16)
+    multimem_allreduce_light_kernel<__nv_bfloat16><<<blocks, kLightThreads, 0, s>>>(m, p, ep, channel, rank, n, n_vec, scale, status, budget_cycles);
+  else if (light)
+    multimem_allreduce_light_kernel<float><<<blocks, kLightThreads, 0, s>>>(m, p, ep, channel, rank, n, n_vec, scale, status, budget_cycles);
+  else if (is_bf16)
+    multimem_allreduce_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(m, p, ep, channel, rank, n, n_vec, scale, status, budget_cycles);
+  else
+    multimem_allreduce_kernel<float><<<blocks, 512, 0, s>>>(m, p, ep, channel, rank, n, n_vec, scale, status, budget_cycles);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + e;
 }

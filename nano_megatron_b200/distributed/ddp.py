@@ -121,11 +121,19 @@ class DistributedDataParallel(nn.Module):
             if ws is not None and self._sync_group_size > 1:
                 # padded to whole 16-byte vectors so the peer kernel takes every bucket
                 per = 16 // torch.empty((), dtype=dtype).element_size()
-                padded = ws.alloc_tensor((b.numel() + per - 1) // per * per, dtype)
-                if padded is not None:
-                    padded.zero_()
-                    b.fused_reduce = ws.make_allreduce_mean(padded)
+                padded_numel = (b.numel() + per - 1) // per * per
+                mapped = ws.alloc_multicast(padded_numel, dtype)
+                if mapped is not None:
+                    # reduced inside the NVSwitch (multimem), each element crosses the links once
+                    padded, mc = mapped
+                    b.fused_reduce = ws.make_multimem_allreduce_mean(padded, mc)
                     flat = padded[: b.numel()]
+                else:
+                    padded = ws.alloc_tensor(padded_numel, dtype)
+                    if padded is not None:
+                        padded.zero_()
+                        b.fused_reduce = ws.make_allreduce_mean(padded)
+                        flat = padded[: b.numel()]
             if flat is None:
                 flat = torch.zeros(b.numel(), dtype=dtype, device=device)
             b.bind_persistent(flat)

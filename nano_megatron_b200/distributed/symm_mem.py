@@ -30,6 +30,9 @@ CHANNEL_TP, CHANNEL_DP, CHANNEL_CP, CHANNEL_AUX = 0, 1, 2, 3
 # with that many blocks (it shares SMs with the backward GEMMs instead of taking
 # them over); positive: the latency-first kernel.
 DDP_ALLREDUCE_BLOCKS = int(os.environ.get("NMB_DDP_AR_BLOCKS", "-148"))
+# The in-switch variant moves half the bytes per GPU and issues one load and one
+# store per 16 bytes, so fewer blocks keep the links busy.
+DDP_MULTIMEM_BLOCKS = int(os.environ.get("NMB_DDP_MM_BLOCKS", "-64"))
 # Arena: tensors up to NMB_SYMM_ARENA_MB MiB (default 256, 0 = off) are carved
 # out of shared symmetric allocations of that size: one IPC handle, one handle
 # exchange and, at teardown, one unmap per peer per arena instead of per tensor
@@ -71,6 +74,9 @@ class SymmetricWorkspace:
         if self.size > self.max_ranks:
             raise RuntimeError(f"group of {self.size} ranks exceeds the kernel limit of {self.max_ranks}")
         self._closed = False
+        self._multicast: list = []
+        self._multicast_bytes = 0
+        self._multicast_failed = False
         self._arena: Optional[SymmetricAllocation] = None
         self._arena_used = 0
         self._allocs: list[SymmetricAllocation] = []
@@ -95,6 +101,7 @@ class SymmetricWorkspace:
                 if r != self.rank and ptr:
                     lib.nmb_symm_close(ctypes.c_void_p(ptr))
         dist.barrier(group=self.group)          # nobody still maps my buffers
+        self._multicast.clear()
         for alloc in self._allocs:
             alloc.bytes = None
             lib.nmb_symm_free(ctypes.c_void_p(alloc.local_ptr))
@@ -268,9 +275,68 @@ class SymmetricWorkspace:
             ctypes.c_int(int(to_all)), native.stream_ptr(self.device))
         native.check_rc(rc, "nmb_embedding_scatter")
 
+    # ------------------------------------------------------------- multimem --
+    def alloc_multicast(self, numel: int, dtype: torch.dtype) -> Optional[tuple[torch.Tensor, int]]:
+        """Collective: a zero-filled tensor that is also mapped at an NVSwitch
+        multicast address on every rank of the group, for in-switch reductions
+        (``multimem.ld_reduce`` / ``multimem.st``).  Allocation and handle
+        exchange are ``torch.distributed``'s symmetric memory (the multicast
+        object needs the driver's virtual-memory API and a file-descriptor
+        exchange between the processes); the kernels that use the address are
+        this package's.  Returns ``(tensor, multicast pointer)``, or ``None``
+        when multicast is not available (switched off with ``NMB_MULTIMEM=0``,
+        no NVSwitch support, a group this rendezvous cannot serve): the caller
+        then uses plain peer memory."""
+        if os.environ.get("NMB_MULTIMEM", "1") == "0" or self._multicast_failed:
+            return None
+        try:
+            import torch.distributed._symmetric_memory as tsm
+            t = tsm.empty(numel, dtype=dtype, device=self.device)
+            handle = tsm.rendezvous(t, self.group)
+            mc = int(handle.multicast_ptr)
+        except Exception:
+            mc = 0
+        # every rank must take the same path
+        flag = torch.tensor([1 if mc else 0], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self._multicast_failed = True
+            return None
+        t.zero_()
+        self._multicast.append((t, handle))
+        self._multicast_bytes += t.numel() * t.element_size()
+        return t, mc
+
+    def multimem_all_reduce_scale_(self, mc: int, numel: int, is_bf16: bool, scale: float, *,
+                                   channel: int = CHANNEL_DP, blocks: int = 64) -> None:
+        """In-place ``sum_over_ranks * scale`` of the buffer mapped at multicast
+        address ``mc`` (from :meth:`alloc_multicast`), reduced inside the switch."""
+        rc = native.lib().nmb_multimem_allreduce_scale(
+            ctypes.c_void_p(mc), self.pad.table(), native.ptr(self.epochs), ctypes.c_int(channel),
+            ctypes.c_int(self.rank), ctypes.c_int(self.size), ctypes.c_longlong(numel), ctypes.c_int(int(is_bf16)),
+            ctypes.c_float(scale), ctypes.c_int(blocks), native.ptr(self.status), ctypes.c_longlong(self.budget),
+            native.stream_ptr(self.device))
+        native.check_rc(rc, "nmb_multimem_allreduce_scale")
+
+    def make_multimem_allreduce_mean(self, flat: torch.Tensor, mc: int) -> Callable[[torch.Tensor, int], bool]:
+        """Reducer for a DDP bucket whose gradients live at the start of ``flat``
+        (a multicast-mapped tensor padded to 16 bytes)."""
+        per = 8 if flat.dtype == torch.bfloat16 else 4
+        if flat.numel() % per != 0:
+            raise ValueError("bucket buffer must be padded to a multiple of 16 bytes")
+        numel, is_bf16 = flat.numel(), flat.dtype == torch.bfloat16
+
+        def reduce(buf: torch.Tensor, divisor: int) -> bool:
+            if buf.data_ptr() != flat.data_ptr() or buf.numel() > numel:
+                return False
+            self.multimem_all_reduce_scale_(mc, numel, is_bf16, 1.0 / divisor, blocks=DDP_MULTIMEM_BLOCKS)
+            return True
+
+        return reduce
+
     def allocated_bytes(self) -> int:
         """Device memory held by this workspace on this rank."""
-        return sum(a.nbytes for a in self._allocs)
+        return sum(a.nbytes for a in self._allocs) + self._multicast_bytes
 
     def make_allreduce_mean(self, flat: torch.Tensor) -> Callable[[torch.Tensor, int], bool]:
         """Reducer for a DDP bucket whose gradients live at the start of ``flat``

@@ -88,6 +88,26 @@ def worker_symm_allreduce():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
+    # in-switch (multimem) variant on a multicast-mapped buffer, where the machine offers it
+    mapped = ws.alloc_multicast(25 * 1024 * 1024 // 2, torch.bfloat16)
+    if mapped is not None:
+        mt, mc = mapped
+        for trial in range(3):
+            src = (torch.randn(mt.numel(), device="cuda") * (ctx.rank + 1 + trial)).to(torch.bfloat16)
+            mt.copy_(src)
+            ref = src.float().clone()
+            dist.all_reduce(ref)
+            ws.multimem_all_reduce_scale_(mc, mt.numel(), True, 1.0 / n)
+            torch.cuda.synchronize()
+            assert (mt.float() - ref / n).abs().max().item() <= 3e-2 * ref.abs().max().item() / n, ("multimem", trial)
+            same = mt.clone()
+            dist.broadcast(same, 0)
+            assert torch.equal(same, mt), "multimem all-reduce results differ between ranks"
+        t_mm = timed(lambda: ws.multimem_all_reduce_scale_(mc, mt.numel(), True, 0.5))
+        if ctx.rank == 0:
+            print(f"PERF allreduce+scale 25MiB x{n}: multimem kernel {t_mm*1e3:.1f} us", flush=True)
+    elif ctx.rank == 0:
+        print("PERF multimem: no multicast support on this machine (peer-memory all-reduce only)", flush=True)
     mine = timed(lambda: ws.all_reduce_scale_(big, 0.5))
     nccl = timed(lambda: (dist.all_reduce(plain), plain.div_(2)))
     if ctx.rank == 0:
