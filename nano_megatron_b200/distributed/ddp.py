@@ -80,6 +80,9 @@ class DistributedDataParallel(nn.Module):
         self._side_stream = torch.cuda.Stream(device=device) if self._overlap else None
         self._side_used = False
         self._flat_buffers: list[torch.Tensor] = []
+        #: buckets in the order their reduction was issued on the side stream this step, and an event after each
+        self._issued: list[GradBucket] = []
+        self._bucket_events: dict[int, torch.cuda.Event] = {}
 
         self._broadcast_params()
         if self._persistent:
@@ -186,6 +189,11 @@ class DistributedDataParallel(nn.Module):
             self._side_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self._side_stream):
                 bucket.sync(self._backend, self._dp_group, self._mean_divisor, group_size=self._sync_group_size)
+                event = self._bucket_events.get(id(bucket))
+                if event is None:
+                    event = self._bucket_events[id(bucket)] = torch.cuda.Event()
+                event.record(self._side_stream)
+            self._issued.append(bucket)
             self._side_used = True
         else:
             bucket.sync(self._backend, self._dp_group, self._mean_divisor, group_size=self._sync_group_size)
@@ -195,16 +203,26 @@ class DistributedDataParallel(nn.Module):
         self._sync_done = False
         return self.module(*args, **kwargs)
 
-    def finish_grad_sync(self) -> None:
-        """Reduce every bucket not reduced yet; idempotent until the next forward/backward."""
+    def finish_grad_sync(self, *, join: bool = True, late_buckets: int = 0) -> list[nn.Parameter]:
+        """Reduce every bucket not reduced yet; idempotent until the next forward/backward.
+
+        With ``join=False`` the compute stream is NOT made to wait for the last
+        ``late_buckets`` reductions issued on the side stream (the buckets that
+        only became complete at the very end of the backward pass: the first
+        layers, the tied embedding): the parameters of those buckets are
+        returned, the caller may work on everything else in the meantime (the
+        optimizer update of the other parameters) and must call
+        :meth:`join_grad_sync` before touching the returned parameters'
+        gradients."""
         if self._sync_done:
-            return
+            return []
         if self._persistent:
             active = True
         else:
             any_grad = any(p.grad is not None for p in self._param_to_bucket)
             any_activity = any(b.coalesced or b.has_pending_ready for b in self._buckets)
             active = any_grad or any_activity
+        late: list[nn.Parameter] = []
         if active:
             for bucket in self._buckets:
                 if bucket.coalesced:
@@ -216,12 +234,32 @@ class DistributedDataParallel(nn.Module):
                         raise RuntimeError(f"finish_grad_sync rank={self._ctx.rank}: missing grads for {names}")
                 self._sync_bucket(bucket)
             if self._side_used:
-                torch.cuda.current_stream().wait_stream(self._side_stream)
-                self._side_used = False
+                cur = torch.cuda.current_stream()
+                keep = min(late_buckets, len(self._issued)) if not join else 0
+                if keep == 0:
+                    cur.wait_stream(self._side_stream)
+                    self._side_used = False
+                else:
+                    # the side stream runs the reductions in order: waiting for the last
+                    # early one covers all before it
+                    early = self._issued[: len(self._issued) - keep]
+                    if early:
+                        cur.wait_event(self._bucket_events[id(early[-1])])
+                    for b in self._issued[len(self._issued) - keep:]:
+                        late.extend(b.params)
             for bucket in self._buckets:
                 bucket.reset()
             self._write_counts.clear()
+            self._issued = []
         self._sync_done = True
+        return late
+
+    def join_grad_sync(self) -> None:
+        """Make the compute stream wait for reductions left running by
+        ``finish_grad_sync(join=False)``."""
+        if self._side_used:
+            torch.cuda.current_stream().wait_stream(self._side_stream)
+            self._side_used = False
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         """With persistent buffers the gradients are zeroed in place (they stay

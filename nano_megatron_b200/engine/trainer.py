@@ -40,6 +40,8 @@ class Trainer:
         self.ddp = DistributedDataParallel(model, ctx, bucket_cap_mb=bucket_cap_mb)
         self.optimizer = AdamW(model.named_parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         self._loss_fn = loss_fn or model.shifted_cross_entropy
+        #: reductions the optimizer update overlaps with (see ``_step_body``)
+        self._late_buckets = 3
         self.device = next(model.parameters()).device
         on_gpu = self.device.type == "cuda"
         self._want_graph = on_gpu if use_cuda_graph is None else (use_cuda_graph and on_gpu)
@@ -91,11 +93,23 @@ class Trainer:
             loss = self._loss_fn(logits, self._labels)
         with nvtx_range("backward"):
             loss.backward()
-        with nvtx_range("grad_sync"):
-            self.ddp.finish_grad_sync()
         if with_optimizer:
+            # The buckets that complete last (first layers, tied embedding) are still
+            # being reduced when backward ends: update all other parameters meanwhile.
+            with nvtx_range("grad_sync"):
+                late = self.ddp.finish_grad_sync(join=False, late_buckets=self._late_buckets)
             with nvtx_range("optimizer"):
-                self.optimizer.step()
+                if late:
+                    ids = {id(p) for p in late}
+                    self.optimizer.step(exclude=ids)
+                    self.ddp.join_grad_sync()
+                    self.optimizer.step(only=ids)
+                else:
+                    self.ddp.join_grad_sync()
+                    self.optimizer.step()
+        else:
+            with nvtx_range("grad_sync"):
+                self.ddp.finish_grad_sync()
         # The loss is handed out in a buffer of its own so that replaying one
         # captured graph never overwrites the value returned by the other.
         self._loss_out.copy_(loss.detach())

@@ -41,7 +41,8 @@ class AdamW:
                 raise TypeError(f"expected Parameter for {name!r}, got {type(param)}")
             names.add(name)
             self._params.append((name, param))
-        self._fused = None  # lazily built device-side plan
+        self._fused = None  # most recently used device-side plan
+        self._plans: dict = {}
 
     # ---------------------------------------------------------------- step --
     def _ensure_state(self, name: str, param: Parameter) -> dict[str, Any]:
@@ -55,8 +56,13 @@ class AdamW:
             self.state[name] = st
         return st
 
-    def step(self) -> None:
-        live = [(n, p) for n, p in self._params if p.grad is not None]
+    def step(self, *, only: "set[int] | None" = None, exclude: "set[int] | None" = None) -> None:
+        """Update every parameter that has a gradient.  ``only`` / ``exclude``
+        (sets of ``id(param)``) restrict the update to a subset, so that a caller
+        can update most parameters while the gradients of the rest are still
+        being reduced, and those afterwards."""
+        live = [(n, p) for n, p in self._params if p.grad is not None
+                and (only is None or id(p) in only) and (exclude is None or id(p) not in exclude)]
         if not live:
             return
         for n, p in live:
@@ -93,11 +99,17 @@ class AdamW:
         from ..ops.adamw import FusedAdamWPlan
 
         key = tuple((n, p.data_ptr(), p.grad.data_ptr()) for n, p in live)
-        if self._fused is None or self._fused.key != key:
+        plan = self._plans.get(key)
+        if plan is None:
+            # a plan per distinct parameter subset (the whole model, or the two halves of a split update)
             states = [self._ensure_state(n, p) for n, p in live]
-            self._fused = FusedAdamWPlan(key, [p for _, p in live], states)
-            self._fused.names = [n for n, _ in live]
-        self._fused.step(self.lr, self.betas, self.eps, self.weight_decay)
+            plan = FusedAdamWPlan(key, [p for _, p in live], states)
+            plan.names = [n for n, _ in live]
+            if len(self._plans) >= 4:
+                self._plans.clear()
+            self._plans[key] = plan
+        self._fused = plan
+        plan.step(self.lr, self.betas, self.eps, self.weight_decay)
         for n, _ in live:
             # `step` is mirrored on the host so state_dict() needs no sync.
             self.state[n]["step"] = int(self.state[n]["step"]) + 1
@@ -115,9 +127,9 @@ class AdamW:
     # ---------------------------------------------------------- state dict --
     def _sync_step_from_device(self) -> None:
         """A replayed CUDA graph advances the device step counter only."""
-        if self._fused is not None:
-            done = int(self._fused.step_count.item())
-            for n in self._fused.names:
+        for plan in self._plans.values():
+            done = int(plan.step_count.item())
+            for n in plan.names:
                 self.state[n]["step"] = done
 
     def state_dict(self) -> dict[str, dict[str, Any]]:
@@ -155,16 +167,22 @@ class AdamW:
         if set(fresh) != set(self.state):
             in_place = False
         self.state = fresh
-        if self._fused is not None and in_place:
-            steps = {int(self.state[n]["step"]) for n in self._fused.names}
-            if len(steps) == 1:
-                self._fused.step_count.fill_(steps.pop())
+        if self._plans and in_place:
+            ok = True
+            for plan in self._plans.values():
+                steps = {int(self.state[n]["step"]) for n in plan.names}
+                if len(steps) == 1:
+                    plan.step_count.fill_(steps.pop())
+                else:
+                    ok = False
+            if ok:
                 return
         self._fused = None
+        self._plans.clear()
 
     def sync_hyper(self) -> None:
         """Push ``lr`` / betas / eps / weight decay to the fused plan's device
         copy if they changed on the host (a plain device copy; call it outside a
         captured graph, before replaying it)."""
-        if self._fused is not None:
-            self._fused.set_hyper(self.lr, self.betas, self.eps, self.weight_decay)
+        for plan in self._plans.values():
+            plan.set_hyper(self.lr, self.betas, self.eps, self.weight_decay)
