@@ -189,7 +189,7 @@ def extra_specs(args) -> list[tuple[str, argparse.Namespace]]:
     else:
         out.append((f"tp{n}+sp-345m", variant(mode="tp", model="345m")))
         out.append((f"cp{n}-1.3b", variant(mode="cp", model="1.3b")))
-    if n in (4, 8):
+    if n in (2, 4, 8):
         out.append((layout(variant(mode="pp"))["name"] + "-345m", variant(mode="pp", model="345m")))
     out.append((f"dp{n}-345m-published-knobs", variant(mode="dp", model="345m", knobs="published")))
     return out
