@@ -63,6 +63,14 @@ struct GemmEpilogue {
   int rope_cols;                // leading columns that hold q and k heads
   int rope_half;                // head_dim / 2
   int swiglu_f;                 // kEpiSwiGLU / kEpiDSwiGLU: F
+  // split-K (weight gradients whose tiles fill a fraction of the machine): the K
+  // range of every tile is cut into `splits` pieces computed by different CTAs;
+  // each stores its fp32 partial tile into `splitk_ws` [tile][split][128][BN], and
+  // the last one to arrive on `splitk_counters[tile]` sums them in split order
+  // (deterministic) and runs the epilogue.
+  float* splitk_ws;
+  unsigned* splitk_counters;
+  int splits;
 };
 
 // Extra epilogue arguments of the C entry points (all optional).
@@ -155,8 +163,9 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarOffset = STAGES * kStageBytes;
-  // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tile_done[2], tmem slot, abort, epoch
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 6) * 8 + 32;
+  // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tile_done[2], decided[2], tmem slot, abort, epoch,
+  // need, last[2]
+  static constexpr int kTotal = kBarOffset + (2 * STAGES + 8) * 8 + 32;
 };
 
 // Copy CTA of the fused all-gather: pulls remote 128-row tiles of A into the
@@ -309,20 +318,42 @@ __device__ __forceinline__ void fused_leave(const FusedComm& fc, uint32_t epoch)
 // alpha / bias / GELU / dGELU / residual / accumulate and stores row `row`.
 // FULL adds the rotary and SwiGLU-backward epilogues (only compiled into the
 // kernel instantiation that also carries the fused collectives).
+// `ws_row` (split-K, last split of a tile): instead of draining TMEM, the values
+// are the sums over the splits of this lane's row in the partial tiles
+// (`ws_row` points at the row in split 0, splits are 128 * BN floats apart).
 template <int BN, bool FULL>
 __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const FusedComm& fc, uint32_t t_row, int row,
-                                                 bool row_ok, int n0, int half, int N) {
+                                                 bool row_ok, int n0, int half, int N, const float* ws_row = nullptr) {
 #pragma unroll 1
   for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
     const int col0 = n0 + c * 32;
     if (col0 >= N) break;  // uniform across the warp
-    uint32_t r[32];
-    tmem_ld_32x32(t_row + c * 32, r);
-    tmem_ld_wait();
-    if (!row_ok) continue;
     float v[32];
+    if (ws_row == nullptr) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + c * 32, r);
+      tmem_ld_wait();
+      if (!row_ok) continue;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
+    } else {
+      if (!row_ok) continue;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0.f;
+      for (int sp = 0; sp < ep.splits; ++sp) {
+        const float4* src = reinterpret_cast<const float4*>(ws_row + static_cast<size_t>(sp) * kBM * BN + c * 32);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 f = __ldcg(src + q);
+          v[4 * q] += f.x;
+          v[4 * q + 1] += f.y;
+          v[4 * q + 2] += f.z;
+          v[4 * q + 3] += f.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= ep.alpha;
+    }
     const bool full_chunk = (col0 + 32 <= N);
     if (full_chunk) {
       if (ep.bias != nullptr) {
@@ -654,7 +685,7 @@ __device__ __forceinline__ void epilogue_columns_reduce(const GemmEpilogue& ep, 
 // CTAs and reduce epilogue of the fused collectives, rotary / SwiGLU
 // epilogues); the plain one stays at the register count that lets a block of
 // the overlapped gradient all-reduce share its SM.
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED, bool SPLITK = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  GemmEpilogue ep, const __grid_constant__ FusedComm fc, int M, int N, int K, int* status) {
@@ -674,11 +705,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + 2;
-  uint64_t* tile_done = acc_empty + 2;  // fused reduce: the 8 epilogue warps have stored a tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_done + 2);
+  uint64_t* tile_done = acc_empty + 2;  // fused reduce / split-K: the 8 epilogue warps have stored a tile
+  uint64_t* decided = tile_done + 2;    // split-K: "is this CTA the last split of the tile" has been decided
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(decided + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* epoch_slot = tmem_slot + 2;
   uint32_t* need_slot = tmem_slot + 3;  // fused reduce: peers must have started a launch with at least this epoch
+  volatile uint32_t* last_slot = tmem_slot + 4;  // split-K, per accumulator buffer: this CTA finishes the tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -686,6 +719,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + kBK - 1) / kBK;
+  // split-K: work unit u = split (u / num_tiles) of tile (u % num_tiles); the splits of
+  // a tile run on different CTAs at the same time
+  const int splits = SPLITK ? ep.splits : 1;
+  const int num_units = num_tiles * splits;
+  const int kb_per_split = (num_kb + splits - 1) / splits;
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: powers of two
   const bool gathered = FUSED && fc.ag_copy_ctas > 0;
   const bool reducing = FUSED && fc.rs_mode != 0;
@@ -721,6 +759,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);  // one arrival per epilogue warp
       mbar_init(&tile_done[b], 8);
+      mbar_init(&decided[b], 1);
     }
     *abort_flag = 0;
     *epoch_slot = fused ? fc.sync[0] + 1 : 0;
@@ -753,7 +792,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       const uint32_t ag_epoch = *epoch_slot;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += n_gemm_ctas) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += n_gemm_ctas) {
+        const int tile = SPLITK ? unit % num_tiles : unit;
+        const int kb_lo = SPLITK ? (unit / num_tiles) * kb_per_split : 0;
+        const int kb_hi = SPLITK ? (kb_lo + kb_per_split < num_kb ? kb_lo + kb_per_split : num_kb) : num_kb;
         int m_blk, n_blk, owner;
         tile_coords(tile, m_blk, n_blk, owner);
         const int m0 = m_blk * kBM;
@@ -772,7 +814,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if (!ok) break;
           fence_proxy_async_all();
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, status, 1)) {
             ok = false;
             break;
@@ -815,13 +857,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += n_gemm_ctas, ++local) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += n_gemm_ctas, ++local) {
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
+        const int kb_lo = SPLITK ? (unit / num_tiles) * kb_per_split : 0;
+        const int kb_hi = SPLITK ? (kb_lo + kb_per_split < num_kb ? kb_lo + kb_per_split : num_kb) : num_kb;
         if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag, status, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, 3)) {
             ok = false;
             break;
@@ -837,7 +881,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                      : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, 8192, 1024)
                                      : make_smem_desc(sb + k * 32, 16, 1024);
-            tc_mma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_bf16(d_tmem, da, db, idesc, ((kb - kb_lo) | k) != 0 ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);  // frees the smem stage once the MMAs have read it
           if (++stage == STAGES) {
@@ -865,10 +909,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           report_status(status, kPeerTimeout, 11);
           *abort_flag = 1;
         }
-        first_tile = num_tiles;
+        first_tile = num_units;
       }
     }
-    for (int tile = first_tile; tile < num_tiles; tile += n_gemm_ctas, ++local) {
+    for (int unit = first_tile; unit < num_units; unit += n_gemm_ctas, ++local) {
+      const int tile = SPLITK ? unit % num_tiles : unit;
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       int m_blk, n_blk, owner;
@@ -880,6 +925,49 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
+      if constexpr (SPLITK) {
+        // pass 1: this split's partial tile -> workspace (fp32, a 128-byte run per lane and chunk)
+        float* ws_tile = ep.splitk_ws + static_cast<size_t>(tile) * splits * kBM * BN;
+        float* mine = ws_tile + (static_cast<size_t>(unit / num_tiles) * kBM + quad * 32 + lane) * BN;
+#pragma unroll 1
+        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          float4* dst = reinterpret_cast<float4*>(mine + c * 32);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            __stcg(dst + q, make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&acc_empty[buf]);
+          mbar_arrive(&tile_done[buf]);
+        }
+        // one thread counts this CTA in; the last split of the tile to arrive finishes it
+        if (warp == 2 && lane == 0) {
+          if (mbar_wait(&tile_done[buf], acc_phase, abort_flag, status, 18)) {
+            __threadfence();
+            const unsigned seen = atomicAdd(&ep.splitk_counters[tile], 1u);
+            const bool last = seen == static_cast<unsigned>(splits) - 1;
+            if (last) ep.splitk_counters[tile] = 0;
+            __threadfence();
+            last_slot[buf] = last ? 1u : 0u;
+          } else {
+            last_slot[buf] = 0u;
+          }
+          mbar_arrive(&decided[buf]);
+        }
+        bool go = true;
+        if (lane == 0) go = mbar_wait(&decided[buf], acc_phase, abort_flag, status, 19);
+        if (!__all_sync(0xffffffffu, go)) break;
+        if (last_slot[buf] != 0u)
+          epilogue_columns<BN, false>(ep, fc, t_row, row, row_ok, n0, half, N,
+                                      ws_tile + static_cast<size_t>(quad * 32 + lane) * BN);
+        continue;
+      }
       if (!reducing) {
         if (FUSED && BN == 256 && ep.mode == kEpiSwiGLU)
           epilogue_swiglu(ep, t_row, row, row_ok, n0, half);
@@ -1268,7 +1356,7 @@ static int launch_gemm_pair(const void* A, int lda, const void* B, int ldb, cons
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED, bool SPLITK = false>
 static int launch_gemm_impl(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
                             int M, int N, int K, int* status, cudaStream_t stream) {
   using L = GemmSmem<BN, STAGES>;
@@ -1299,9 +1387,9 @@ static int launch_gemm_impl(const void* A, int lda, const void* B, int ldb, cons
   }
   if (rc != 0) return 200 + rc;
 
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, FUSED>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, FUSED, SPLITK>;
   const int smem_bytes = L::kTotal + 1024 + (fc.rs_mode != 0 ? kEpiStageBytes : 0);
-  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) * (SPLITK ? ep.splits : 1);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (fc.ag_copy_ctas > 0) {
     // the copy CTAs take SMs of their own; everything must be co-resident
@@ -1326,10 +1414,48 @@ static int launch_gemm(const void* A, int lda, const void* B, int ldb, const Gem
   return launch_gemm_impl<BN, STAGES, A_MN, B_MN, false>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
 }
 
+// Split-K workspace of each device (registered by the host program: the launchers
+// allocate nothing).  One workspace per device: split-K launches of one device
+// must be ordered on one stream.
+constexpr int kMaxDevices = 64;
+static float* g_splitk_ws[kMaxDevices] = {nullptr};
+static long long g_splitk_ws_bytes[kMaxDevices] = {0};
+static unsigned* g_splitk_counters[kMaxDevices] = {nullptr};
+static int g_splitk_n_counters[kMaxDevices] = {0};
+
+// How many ways to cut K so that tiles * splits comes close to filling the SMs:
+// only for GEMMs whose tiles fill less than half of the machine and whose K is
+// long enough that a split still has >= 8 k-blocks to amortise its epilogue.
+static int choose_splits(int tiles, int num_kb, int dev) {
+  if (dev < 0 || dev >= kMaxDevices || g_splitk_ws[dev] == nullptr) return 1;
+  if (tiles * 2 > sm_count() || num_kb < 16 || tiles > g_splitk_n_counters[dev]) return 1;
+  int s = sm_count() / tiles;
+  if (s > num_kb / 8) s = num_kb / 8;
+  if (s > 8) s = 8;
+  while (s > 1 && static_cast<long long>(tiles) * s * kBM * 256 * 4 > g_splitk_ws_bytes[dev]) --s;
+  return s < 2 ? 1 : s;
+}
+
 template <bool A_MN, bool B_MN>
 static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const GemmEpilogue& ep, const FusedComm& fc,
                          int M, int N, int K, int* status, cudaStream_t stream) {
   if (ep.mode == kEpiSwiGLU) return launch_gemm<256, 4, A_MN, B_MN>(A, lda, B, ldb, ep, fc, M, N, K, status, stream);
+  if constexpr (A_MN && B_MN) {
+    // weight gradients: K is the token count, the output is small
+    if (fc.ag_copy_ctas == 0 && fc.rs_mode == 0 && ep.mode == kEpiPlain && N > 128) {
+      int dev = -1;
+      cudaGetDevice(&dev);
+      const int tiles = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
+      const int splits = choose_splits(tiles, (K + kBK - 1) / kBK, dev);
+      if (splits > 1) {
+        GemmEpilogue eps = ep;
+        eps.splits = splits;
+        eps.splitk_ws = g_splitk_ws[dev];
+        eps.splitk_counters = g_splitk_counters[dev];
+        return launch_gemm_impl<256, 4, A_MN, B_MN, false, true>(A, lda, B, ldb, eps, fc, M, N, K, status, stream);
+      }
+    }
+  }
   if (g_pair_enabled && fc.ag_copy_ctas == 0 && fc.rs_mode == 0 && N >= 256 && ep.mode < kEpiRope) {
     const int pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
     if (pair_tiles * 3 >= sm_count() / 2)
@@ -1381,9 +1507,29 @@ static int configure_gemm_pair() {
 // Opt every GEMM variant in to its dynamic shared memory size on the current
 // device.  Called once per process (per device) right after the library is
 // loaded, from the thread that loads it.
+// Register (or, with null pointers, withdraw) the split-K workspace of the current
+// device: `ws_bytes` of fp32 scratch and `n_counters` zero-initialised 32-bit
+// counters, both owned by the caller for as long as GEMMs are launched.
+extern "C" int nmb_gemm_set_splitk_workspace(void* ws, long long ws_bytes, void* counters, int n_counters) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= nmb::kMaxDevices) return nmb::kBadArgument;
+  nmb::g_splitk_ws[dev] = static_cast<float*>(ws);
+  nmb::g_splitk_ws_bytes[dev] = ws_bytes;
+  nmb::g_splitk_counters[dev] = static_cast<unsigned*>(counters);
+  nmb::g_splitk_n_counters[dev] = n_counters;
+  return 0;
+}
+
 extern "C" int nmb_gemm_configure() {
   using namespace nmb;
   int rc = 0;
+  {
+    auto kern = gemm_bf16_kernel<256, 4, true, true, false, true>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256, 4>::kTotal + 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) rc |= 300 + static_cast<int>(e);
+  }
   rc |= configure_gemm<256, 4, false, false>();
   rc |= configure_gemm<256, 4, false, true>();
   rc |= configure_gemm<256, 4, true, true>();
@@ -1439,6 +1585,9 @@ static int gemm_entry(const void* A, int lda, int a_mn, const void* B, int ldb, 
   ep.rope_cols = extra != nullptr ? extra->rope_cols : 0;
   ep.rope_half = extra != nullptr ? extra->rope_half : 0;
   ep.swiglu_f = extra != nullptr ? extra->swiglu_f : 0;
+  ep.splits = 1;
+  ep.splitk_ws = nullptr;
+  ep.splitk_counters = nullptr;
   if (mode == kEpiRope) {
     // whole 32-column chunks inside one head, 16-byte aligned table rows
     if (ep.rope_table == nullptr || ep.rope_pos == nullptr || ep.rope_half < 16 || (ep.rope_half % 16) != 0 ||

@@ -36,6 +36,8 @@ def available() -> bool:
 
 
 _configured_devices: set[int] = set()
+_SPLITK_WS_BYTES = 64 << 20
+_splitk_keep: dict[int, tuple] = {}
 
 
 def _configure_current_device(loaded: ctypes.CDLL) -> None:
@@ -51,6 +53,16 @@ def _configure_current_device(loaded: ctypes.CDLL) -> None:
         rc = fn()
         if rc != 0:
             raise NativeKernelError(f"kernel configuration failed with code {rc} on device {dev}")
+    if os.environ.get("NMB_SPLITK", "1") != "0":
+        # scratch of the split-K weight-gradient GEMMs (fp32 partial tiles + per-tile counters),
+        # registered once per device so that the launchers never allocate
+        ws = torch.empty(_SPLITK_WS_BYTES // 4, dtype=torch.float32, device=torch.device("cuda", dev))
+        counters = torch.zeros(1024, dtype=torch.int32, device=torch.device("cuda", dev))
+        rc = loaded.nmb_gemm_set_splitk_workspace(ctypes.c_void_p(ws.data_ptr()), ctypes.c_longlong(_SPLITK_WS_BYTES),
+                                                  ctypes.c_void_p(counters.data_ptr()), ctypes.c_int(counters.numel()))
+        if rc != 0:
+            raise NativeKernelError(f"split-K workspace registration failed with code {rc} on device {dev}")
+        _splitk_keep[dev] = (ws, counters)
     _configured_devices.add(dev)
 
 

@@ -192,3 +192,28 @@ def test_swiglu_epilogues(m, f, k, with_bias):
     assert _rel(w1.grad, w1f.grad) < 3e-2 and _rel(w2.grad, w2f.grad) < 3e-2
     if with_bias:
         assert _rel(b1.grad, b1f.grad) < 3e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 1024, 4096), (768, 512, 2048), (3072, 1024, 4096), (256, 384, 8192)])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_split_k_weight_gradient(m, n, k, accumulate):
+    """Weight-gradient layout (both operands MN-major) with few output tiles and a
+    long K: the K range is split over CTAs, partial tiles are summed by the last
+    split of a tile in split order.  Same result as fp32, bit-identical from run
+    to run, and accumulation into an existing gradient works."""
+    from nano_megatron_b200.ops import native
+    from nano_megatron_b200.ops.gemm import gemm_bf16
+
+    torch.manual_seed(3)
+    a, b = _rand((k, m), 0.3), _rand((k, n), 0.3)
+    base = _rand((m, n), 1.0)
+    ref = a.float().t() @ b.float() + (base.float() if accumulate else 0.0)
+    outs = []
+    for _ in range(3):
+        out = base.clone() if accumulate else torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        gemm_bf16(a, b, a_mn=True, b_mn=True, out=out, accumulate=accumulate)
+        outs.append(out)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert _rel(outs[0], ref) < 1e-2
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
