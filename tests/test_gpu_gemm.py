@@ -209,11 +209,15 @@ def test_split_k_weight_gradient(m, n, k, accumulate):
     base = _rand((m, n), 1.0)
     ref = a.float().t() @ b.float() + (base.float() if accumulate else 0.0)
     outs = []
-    for _ in range(3):
-        out = base.clone() if accumulate else torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-        gemm_bf16(a, b, a_mn=True, b_mn=True, out=out, accumulate=accumulate)
-        outs.append(out)
-    torch.cuda.synchronize()
+    native.enable_split_k(torch.cuda.current_device(), True)      # off by default
+    try:
+        for _ in range(3):
+            out = base.clone() if accumulate else torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            gemm_bf16(a, b, a_mn=True, b_mn=True, out=out, accumulate=accumulate)
+            outs.append(out)
+        torch.cuda.synchronize()
+    finally:
+        native.enable_split_k(torch.cuda.current_device(), False)
     native.check_status()
     assert _rel(outs[0], ref) < 1e-2
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
