@@ -313,6 +313,42 @@ __device__ __forceinline__ void fused_leave(const FusedComm& fc, uint32_t epoch)
   }
 }
 
+// Store of one 32-column bf16 chunk of a warp's 32 accumulator rows.  In the
+// accumulator a lane owns a row, so a store from registers writes 16 bytes to 32
+// different rows per instruction (half-filled sectors, four instructions per
+// chunk).  With a staging buffer the warp transposes the chunk through 2 KB of
+// shared memory of its own (16-byte pieces XOR-swizzled so that both phases are
+// free of bank conflicts) and writes 8 rows x 64 contiguous bytes per
+// instruction.  `dst` points at column 0 of the chunk in the warp's first row;
+// rows >= rows_valid are not written.  All 32 lanes must call it.
+struct ChunkStore {
+  uint4* wbuf;
+  int lane;
+  __nv_bfloat16* dst;
+  size_t ld;
+  int rows_valid;
+  // 16-byte piece q (of 4) of this lane's row
+  __device__ __forceinline__ void put(int q, const uint4& o) const {
+    if (wbuf != nullptr) {
+      wbuf[lane * 4 + (q ^ ((lane >> 1) & 3))] = o;
+    } else if (lane < rows_valid) {
+      reinterpret_cast<uint4*>(dst + static_cast<size_t>(lane) * ld)[q] = o;
+    }
+  }
+  __device__ __forceinline__ void flush() const {
+    if (wbuf == nullptr) return;
+    __syncwarp();
+    const int seg = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i * 8 + (lane >> 2);
+      const uint4 u = wbuf[r * 4 + (seg ^ ((r >> 1) & 3))];
+      if (r < rows_valid) *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * ld + seg * 8) = u;
+    }
+    __syncwarp();
+  }
+};
+
 // Epilogue of one 128-row accumulator tile for one warp: drains its half of
 // the BN columns of TMEM lane quadrant `t_row` (32 columns at a time), applies
 // alpha / bias / GELU / dGELU / residual / accumulate and stores row `row`.
@@ -323,7 +359,19 @@ __device__ __forceinline__ void fused_leave(const FusedComm& fc, uint32_t epoch)
 // (`ws_row` points at the row in split 0, splits are 128 * BN floats apart).
 template <int BN, bool FULL>
 __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const FusedComm& fc, uint32_t t_row, int row,
-                                                 bool row_ok, int n0, int half, int N, const float* ws_row = nullptr) {
+                                                 bool row_ok, int n0, int half, int N, const float* ws_row = nullptr,
+                                                 uint4* wbuf = nullptr, int lane = 0, int M = 0) {
+  // With a staging buffer every lane takes part in every store: a lane whose row
+  // lies beyond M works on the last valid row instead (its result is not written).
+  const bool staged = wbuf != nullptr && !ep.out_f32 && (N % 32) == 0;
+  if (!staged) wbuf = nullptr;
+  const int wrow0 = row - (staged ? lane : 0);  // first row of the warp (staged) / this lane's row (direct)
+  const int rows_valid = staged ? (M - wrow0 < 32 ? M - wrow0 : 32) : 32;
+  if (staged && !row_ok) {
+    row = M - 1;
+    row_ok = true;
+  }
+  const int slane = staged ? lane : 0;
 #pragma unroll 1
   for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
     const int col0 = n0 + c * 32;
@@ -387,7 +435,11 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
       if (FULL && ep.mode == kEpiDSwiGLU) {
         // v = d(act); gate / up pre-activations from the forward pass
         const __nv_bfloat16* pre = ep.aux_in + static_cast<size_t>(row) * ep.ld_aux + col0;
-        __nv_bfloat16* c_row = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc + col0;
+        // two output streams: d gate now, d up kept in registers until the buffer is free again
+        __nv_bfloat16* c0 = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(wrow0) * ep.ldc + col0;
+        const ChunkStore sg{wbuf, slane, c0, static_cast<size_t>(ep.ldc), rows_valid};
+        const ChunkStore su{wbuf, slane, c0 + ep.swiglu_f, static_cast<size_t>(ep.ldc), rows_valid};
+        uint4 ou4[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const uint4 gu = reinterpret_cast<const uint4*>(pre)[q];
@@ -404,22 +456,23 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
             og[t] = pack_bf16x2(d0 * u.x * s0 * (1.f + g.x * (1.f - s0)), d1 * u.y * s1 * (1.f + g.y * (1.f - s1)));
             ou[t] = pack_bf16x2(d0 * g.x * s0, d1 * g.y * s1);
           }
-          reinterpret_cast<uint4*>(c_row)[q] = make_uint4(og[0], og[1], og[2], og[3]);
-          reinterpret_cast<uint4*>(c_row + ep.swiglu_f)[q] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+          sg.put(q, make_uint4(og[0], og[1], og[2], og[3]));
+          ou4[q] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
         }
+        sg.flush();
+#pragma unroll
+        for (int q = 0; q < 4; ++q) su.put(q, ou4[q]);
+        su.flush();
         continue;
       }
       if (ep.mode == kEpiGelu) {
-        uint4* ap = reinterpret_cast<uint4*>(ep.aux_out + static_cast<size_t>(row) * ep.ld_aux + col0);
+        const ChunkStore sa{wbuf, slane, ep.aux_out + static_cast<size_t>(wrow0) * ep.ld_aux + col0,
+                            static_cast<size_t>(ep.ld_aux), rows_valid};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 u;
-          u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-          u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-          u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-          u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-          ap[q] = u;
-        }
+        for (int q = 0; q < 4; ++q)
+          sa.put(q, make_uint4(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]), pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]),
+                               pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7])));
+        sa.flush();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           // GELU of the value the backward pass will see (bf16-rounded).
@@ -474,6 +527,8 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
       } else {
         __nv_bfloat16* c_row = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc;
         uint4* cp = reinterpret_cast<uint4*>(c_row + col0);
+        const ChunkStore sc{wbuf, slane, static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(wrow0) * ep.ldc + col0,
+                            static_cast<size_t>(ep.ldc), rows_valid};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           if (ep.accumulate) {
@@ -486,13 +541,10 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
               v[q * 8 + t * 2 + 1] += f.y;
             }
           }
-          uint4 o;
-          o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-          o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-          o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-          o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-          cp[q] = o;
+          sc.put(q, make_uint4(pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]), pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]),
+                               pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7])));
         }
+        sc.flush();
       }
     } else {
       // Ragged last chunk of the N dimension: scalar path.
@@ -530,8 +582,11 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
 // (what the backward pass needs) and silu(gate) * up into C.  The activation is
 // computed from the bf16-rounded pre-activations, as the backward will see them.
 __device__ __forceinline__ void epilogue_swiglu(const GemmEpilogue& ep, uint32_t t_row, int row, bool row_ok, int n0,
-                                                int half) {
+                                                int half, uint4* wbuf, int lane, int M) {
   const int F = ep.swiglu_f;
+  const int wrow0 = row - lane;
+  const int rows_valid = M - wrow0 < 32 ? M - wrow0 : 32;
+  (void)row_ok;
 #pragma unroll 1
   for (int c = 2 * half; c < 2 * half + 2; ++c) {
     const int col0 = (n0 >> 1) + c * 32;
@@ -540,9 +595,12 @@ __device__ __forceinline__ void epilogue_swiglu(const GemmEpilogue& ep, uint32_t
     tmem_ld_32x32(t_row + c * 32, rg);
     tmem_ld_32x32(t_row + 128 + c * 32, ru);
     tmem_ld_wait();
-    if (!row_ok) continue;
-    __nv_bfloat16* pre = ep.aux_out + static_cast<size_t>(row) * ep.ld_aux + col0;
-    __nv_bfloat16* act = static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(row) * ep.ldc + col0;
+    __nv_bfloat16* pre = ep.aux_out + static_cast<size_t>(wrow0) * ep.ld_aux + col0;
+    const ChunkStore sg{wbuf, lane, pre, static_cast<size_t>(ep.ld_aux), rows_valid};
+    const ChunkStore su{wbuf, lane, pre + F, static_cast<size_t>(ep.ld_aux), rows_valid};
+    const ChunkStore sa{wbuf, lane, static_cast<__nv_bfloat16*>(ep.c) + static_cast<size_t>(wrow0) * ep.ldc + col0,
+                        static_cast<size_t>(ep.ldc), rows_valid};
+    uint4 pu4[4], pa4[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float g[8], u[8];
@@ -575,10 +633,17 @@ __device__ __forceinline__ void epilogue_swiglu(const GemmEpilogue& ep, uint32_t
         const float2 ur = unpack_bf16x2(pu[t]);
         pa[t] = pack_bf16x2(gr.x / (1.f + __expf(-gr.x)) * ur.x, gr.y / (1.f + __expf(-gr.y)) * ur.y);
       }
-      reinterpret_cast<uint4*>(pre)[q] = make_uint4(pg[0], pg[1], pg[2], pg[3]);
-      reinterpret_cast<uint4*>(pre + F)[q] = make_uint4(pu[0], pu[1], pu[2], pu[3]);
-      reinterpret_cast<uint4*>(act)[q] = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+      sg.put(q, make_uint4(pg[0], pg[1], pg[2], pg[3]));
+      pu4[q] = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+      pa4[q] = make_uint4(pa[0], pa[1], pa[2], pa[3]);
     }
+    sg.flush();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) su.put(q, pu4[q]);
+    su.flush();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) sa.put(q, pa4[q]);
+    sa.flush();
   }
 }
 
@@ -685,10 +750,9 @@ __device__ __forceinline__ void epilogue_columns_reduce(const GemmEpilogue& ep, 
 // CTAs and reduce epilogue of the fused collectives, rotary / SwiGLU
 // epilogues); the plain one stays at the register count that lets a block of
 // the overlapped gradient all-reduce share its SM.
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED, bool SPLITK = false>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 GemmEpilogue ep, const __grid_constant__ FusedComm fc, int M, int N, int K, int* status) {
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED, bool SPLITK>
+__device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tma_a, const CUtensorMap& tma_b, const GemmEpilogue& ep,
+                                               const FusedComm& fc, int M, int N, int K, int* status) {
   using L = GemmSmem<BN, STAGES>;
   const int n_gemm_ctas = FUSED ? gridDim.x - fc.ag_copy_ctas : gridDim.x;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -970,9 +1034,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       if (!reducing) {
         if (FUSED && BN == 256 && ep.mode == kEpiSwiGLU)
-          epilogue_swiglu(ep, t_row, row, row_ok, n0, half);
+          epilogue_swiglu(ep, t_row, row, row_ok, n0, half,
+                          reinterpret_cast<uint4*>(smem + L::kTotal) + (warp - 2) * 256, lane, M);
         else
-          epilogue_columns<BN, FUSED>(ep, fc, t_row, row, row_ok, n0, half, N);
+          epilogue_columns<BN, FUSED>(ep, fc, t_row, row, row_ok, n0, half, N, nullptr,
+                                      reinterpret_cast<uint4*>(smem + L::kTotal) + (warp - 2) * 256, lane, M);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -1048,6 +1114,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   if (fused) fused_leave(fc, *epoch_slot);
 }
 
+// Two entry points around one body.  The plain GEMM is capped at 144 registers per
+// thread: with 10 warps that leaves room on every SM sub-partition for one warp
+// of the overlapped gradient all-reduce (<= 80 registers), which is what lets a
+// block of it share the SM with a resident GEMM CTA.  The instantiation that
+// carries the fused collectives, the rotary / SwiGLU epilogues or split-K may use
+// what `__launch_bounds__` allows.
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __maxnreg__(144)
+gemm_plain_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, GemmEpilogue ep,
+                  const __grid_constant__ FusedComm fc, int M, int N, int K, int* status) {
+  gemm_bf16_body<BN, STAGES, A_MN, B_MN, false, false>(tma_a, tma_b, ep, fc, M, N, K, status);
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED, bool SPLITK = false>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 GemmEpilogue ep, const __grid_constant__ FusedComm fc, int M, int N, int K, int* status) {
+  gemm_bf16_body<BN, STAGES, A_MN, B_MN, FUSED, SPLITK>(tma_a, tma_b, ep, fc, M, N, K, status);
+}
+
 // ---------------------------------------------------------------------------
 // CTA-pair variant (tcgen05.mma.cta_group::2): a cluster of two CTAs computes a
 // 256 x 256 tile.  Each CTA loads its own 128 rows of A and its own 128 rows
@@ -1087,7 +1173,7 @@ struct GemmPairSmem {
 };
 
 template <bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __maxnreg__(144)  // same cap and reason as gemm_plain_kernel
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  GemmEpilogue ep, const __grid_constant__ FusedComm fc, int M, int N, int K, int* status) {
   using L = GemmPairSmem;
@@ -1274,7 +1360,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
-      epilogue_columns<BN, false>(ep, fc, t_row, row, row_ok, n0, half, N);
+      epilogue_columns<BN, false>(ep, fc, t_row, row, row_ok, n0, half, N, nullptr,
+                                  reinterpret_cast<uint4*>(smem + L::kTotal) + (warp - 2) * 256, lane, M);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty[buf], 0));
@@ -1330,7 +1417,7 @@ static int launch_gemm_pair(const void* A, int lda, const void* B, int ldb, cons
   auto kern = gemm_pair_kernel<A_MN, B_MN>;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kGemmThreads);
-  cfg.dynamicSmemBytes = L::kTotal + 1024;
+  cfg.dynamicSmemBytes = L::kTotal + 1024 + kEpiStageBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1387,8 +1474,12 @@ static int launch_gemm_impl(const void* A, int lda, const void* B, int ldb, cons
   }
   if (rc != 0) return 200 + rc;
 
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, FUSED, SPLITK>;
-  const int smem_bytes = L::kTotal + 1024 + (fc.rs_mode != 0 ? kEpiStageBytes : 0);
+  void (*kern)(CUtensorMap, CUtensorMap, GemmEpilogue, FusedComm, int, int, int, int*);
+  if constexpr (!FUSED && !SPLITK)
+    kern = gemm_plain_kernel<BN, STAGES, A_MN, B_MN>;
+  else
+    kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, FUSED, SPLITK>;
+  const int smem_bytes = L::kTotal + 1024 + kEpiStageBytes;
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) * (SPLITK ? ep.splits : 1);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (fc.ag_copy_ctas > 0) {
@@ -1473,9 +1564,13 @@ static int dispatch_tile(const void* A, int lda, const void* B, int ldb, const G
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool FUSED>
 static int configure_gemm_impl() {
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, FUSED>;
+  void (*kern)(CUtensorMap, CUtensorMap, GemmEpilogue, FusedComm, int, int, int, int*);
+  if constexpr (!FUSED)
+    kern = gemm_plain_kernel<BN, STAGES, A_MN, B_MN>;
+  else
+    kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, FUSED>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       GemmSmem<BN, STAGES>::kTotal + 1024 + (FUSED ? kEpiStageBytes : 0));
+                                       GemmSmem<BN, STAGES>::kTotal + 1024 + kEpiStageBytes);
   // Every large kernel of the library asks for the maximum shared-memory
   // carve-out, and so do the communication kernels meant to run beside them: an
   // SM keeps one carve-out at a time, so kernels that prefer different ones
@@ -1495,7 +1590,7 @@ static int configure_gemm() {
 template <bool A_MN, bool B_MN>
 static int configure_gemm_pair() {
   cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       GemmPairSmem::kTotal + 1024);
+                                       GemmPairSmem::kTotal + 1024 + kEpiStageBytes);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(gemm_pair_kernel<A_MN, B_MN>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
@@ -1525,7 +1620,7 @@ extern "C" int nmb_gemm_configure() {
   int rc = 0;
   {
     auto kern = gemm_bf16_kernel<256, 4, true, true, false, true>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256, 4>::kTotal + 1024);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256, 4>::kTotal + 1024 + kEpiStageBytes);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) rc |= 300 + static_cast<int>(e);

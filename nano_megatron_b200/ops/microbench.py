@@ -70,6 +70,20 @@ def bench_gemm(args) -> None:
         _report("gemm wgrad layout (A, B MN-major)", _timed(lambda: gemm_bf16(at, bt, a_mn=True, b_mn=True), args.iters), flops)
         _report("gemm + bias + GELU epilogue", _timed(lambda: gemm_bf16(a, b, bias=bias, mode=EPI_GELU, aux_out=aux), args.iters), flops)
         _report("torch.matmul (cuBLAS)", _timed(lambda: torch.matmul(a, b.t()), args.iters), flops)
+    if args.epilogues:
+        # the epilogue-fused GEMMs of the RoPE / SwiGLU model: QKV + rotary, fc1 + SwiGLU, fc2 dgrad + SwiGLU backward
+        from .gemm import EPI_DSWIGLU, EPI_ROPE, EPI_SWIGLU, RopeSpec
+        d = 64
+        inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, device="cuda").float() / d))
+        pos = (torch.arange(m, device="cuda") % 2048).contiguous()
+        spec = RopeSpec(RopeSpec.make_table(inv, 2048), pos, (n // 3 * 2) // d * d)
+        _report("gemm + rotary epilogue (q, k of a packed QKV)", _timed(lambda: gemm_bf16(a, b, mode=EPI_ROPE, rope=spec), args.iters), flops)
+        pre = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        _report("gemm + SwiGLU epilogue (B = [gate; up])", _timed(lambda: gemm_bf16(a, b, mode=EPI_SWIGLU, aux_out=pre), args.iters), flops)
+        dy = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        w2 = torch.randn(k, n // 2, device="cuda").to(torch.bfloat16)       # fc2 weight [H, F]
+        _report("dgrad gemm + SwiGLU-backward epilogue", _timed(lambda: gemm_bf16(dy, w2, b_mn=True, mode=EPI_DSWIGLU, aux_in=pre), args.iters),
+                2.0 * m * (n // 2) * k)
 
 
 def bench_attn(args) -> None:
@@ -108,7 +122,11 @@ def bench_ce(args) -> None:
     lse, _, _ = kernels.ce_combine(stats.unsqueeze(0), tgt, -100)
     gs = torch.ones(1, device="cuda")
     dl = torch.empty_like(logits)
-    _report(f"cross-entropy stats {r}x{v}", _timed(lambda: kernels.ce_stats(logits, tgt, 0), args.iters), nbytes=2.0 * r * v)
+    ex = kernels.CeExchange(r, logits.device)
+    _report(f"cross-entropy forward, one launch {r}x{v}",
+            _timed(lambda: kernels.ce_forward_fused(logits, tgt, 0, -100, ex), args.iters), nbytes=2.0 * r * v)
+    _report(f"cross-entropy stats (two-pass kernel of the NCCL path) {r}x{v}",
+            _timed(lambda: kernels.ce_stats(logits, tgt, 0), args.iters), nbytes=2.0 * r * v)
     _report("cross-entropy backward", _timed(lambda: kernels.ce_bwd(logits, tgt, 0, -100, lse, gs, out=dl), args.iters),
             nbytes=4.0 * r * v)
 
@@ -132,6 +150,7 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--variants", action="store_true")
+    ap.add_argument("--epilogues", action="store_true", help="gemm: also time the rotary / SwiGLU epilogue GEMMs")
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16)
