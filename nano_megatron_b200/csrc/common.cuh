@@ -216,6 +216,28 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar_addr)
                : "memory");
 }
+// The same arrival on the barrier at this offset in BOTH CTAs of the pair: the
+// hardware signals the two barriers itself, so no thread has to pass a release
+// on to the other CTA.
+__device__ __forceinline__ void tc_commit_pair_both(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+// Tiled load of this CTA's own tile into its own shared memory whose byte count
+// completes on a barrier of either CTA of the pair (`bar_cluster_addr`, from
+// cluster_addr()): both CTAs count on the even CTA's barrier, which is the one
+// the MMA issuer waits on.  One destination CTA per load.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
 // D[tmem of both CTAs] (+)= A[256 x 16, 128 rows per CTA] * B[N x 16, N/2 rows per CTA]
 __device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                  uint32_t accumulate) {

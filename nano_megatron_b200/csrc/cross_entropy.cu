@@ -138,6 +138,12 @@ struct CeComm {
   long long budget;
 };
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
   const float mm = fmaxf(m, m2);
   // exp(-inf - -inf) would be NaN: an empty partner contributes nothing
@@ -161,9 +167,15 @@ ce_forward_fused_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, 
   const bool vec = (vloc % 8 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
   float m = -INFINITY, s = 0.f;
   if (vec) {
+    // Four independent 16-byte loads in flight per thread (one row is ~100 KB and
+    // the kernel is otherwise bound by load latency), then one FFMA + ex2 per
+    // element: exp(f - m) = 2^(f * log2e - m * log2e).
     const uint4* xv = reinterpret_cast<const uint4*>(x);
-    for (int i = threadIdx.x; i < vloc / 8; i += blockDim.x) {
-      const uint4 u = xv[i];
+    const int nvec = vloc / 8;
+    const int step = blockDim.x;
+    constexpr float kLog2e = 1.4426950408889634f;
+    float ml = -INFINITY;  // m * log2e
+    auto take = [&](const uint4& u) {
       const uint32_t w[4] = {u.x, u.y, u.z, u.w};
       float f[8];
 #pragma unroll
@@ -176,12 +188,22 @@ ce_forward_fused_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, 
 #pragma unroll
       for (int t = 1; t < 8; ++t) m8 = fmaxf(m8, f[t]);
       if (m8 > m) {
-        s *= __expf(m - m8);  // m == -inf: s is 0 and exp(-inf) = 0
+        s *= fast_exp2(ml - m8 * kLog2e);  // m == -inf: s is 0 and 2^(-inf) = 0
         m = m8;
+        ml = m8 * kLog2e;
       }
 #pragma unroll
-      for (int t = 0; t < 8; ++t) s += __expf(f[t] - m);
+      for (int t = 0; t < 8; ++t) s += fast_exp2(fmaf(f[t], kLog2e, -ml));
+    };
+    int i = threadIdx.x;
+    for (; i + 3 * step < nvec; i += 4 * step) {
+      uint4 u[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) u[j] = xv[i + j * step];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) take(u[j]);
     }
+    for (; i < nvec; i += step) take(xv[i]);
   } else {
     for (int i = threadIdx.x; i < vloc; i += blockDim.x) {
       const float v = __bfloat162float(x[i]);

@@ -65,9 +65,9 @@ struct GemmEpilogue {
   int swiglu_f;                 // kEpiSwiGLU / kEpiDSwiGLU: F
   // split-K (weight gradients whose tiles fill a fraction of the machine): the K
   // range of every tile is cut into `splits` pieces computed by different CTAs;
-  // each stores its fp32 partial tile into `splitk_ws` [tile][split][128][BN], and
-  // the last one to arrive on `splitk_counters[tile]` sums them in split order
-  // (deterministic) and runs the epilogue.
+  // all but the last store their fp32 partial tile into `splitk_ws` [tile][split][128 * BN]
+  // and count themselves in on `splitk_counters[tile]`; the last split adds them to
+  // its own accumulator in split order (deterministic) and runs the epilogue.
   float* splitk_ws;
   unsigned* splitk_counters;
   int splits;
@@ -354,9 +354,10 @@ struct ChunkStore {
 // alpha / bias / GELU / dGELU / residual / accumulate and stores row `row`.
 // FULL adds the rotary and SwiGLU-backward epilogues (only compiled into the
 // kernel instantiation that also carries the fused collectives).
-// `ws_row` (split-K, last split of a tile): instead of draining TMEM, the values
-// are the sums over the splits of this lane's row in the partial tiles
-// (`ws_row` points at the row in split 0, splits are 128 * BN floats apart).
+// `ws_row` (split-K, last split of a tile): the other splits' partial tiles are added
+// to this split's own part in TMEM, in split order.  It points at this lane's first
+// float4 of split 0's partial (layout [chunk][quad][q][lane] float4, so a warp reads
+// 512-byte runs); splits are 128 * BN floats apart.
 template <int BN, bool FULL>
 __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const FusedComm& fc, uint32_t t_row, int row,
                                                  bool row_ok, int n0, int half, int N, const float* ws_row = nullptr,
@@ -377,30 +378,46 @@ __device__ __forceinline__ void epilogue_columns(const GemmEpilogue& ep, const F
     const int col0 = n0 + c * 32;
     if (col0 >= N) break;  // uniform across the warp
     float v[32];
-    if (ws_row == nullptr) {
+    {
       uint32_t r[32];
       tmem_ld_32x32(t_row + c * 32, r);
-      tmem_ld_wait();
-      if (!row_ok) continue;
+      if (ws_row != nullptr) {
+        // split-K: the other splits' partials, two splits' loads in flight at a time
+        const float4* src = reinterpret_cast<const float4*>(ws_row) + c * 1024;
+        float4 f[8];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
-    } else {
-      if (!row_ok) continue;
+        for (int q = 0; q < 8; ++q) f[q] = __ldcg(src + q * 32);
+        tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = 0.f;
-      for (int sp = 0; sp < ep.splits; ++sp) {
-        const float4* src = reinterpret_cast<const float4*>(ws_row + static_cast<size_t>(sp) * kBM * BN + c * 32);
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        for (int sp = 0; sp < ep.splits - 1; ++sp) {
+          float4 g[8];
+          const bool more = sp + 2 < ep.splits;
+          if (more) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float4 f = __ldcg(src + q);
-          v[4 * q] += f.x;
-          v[4 * q + 1] += f.y;
-          v[4 * q + 2] += f.z;
-          v[4 * q + 3] += f.w;
+            for (int q = 0; q < 8; ++q) g[q] = __ldcg(src + static_cast<size_t>(sp + 1) * (kBM * BN / 4) + q * 32);
+          }
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            v[4 * q] += f[q].x;
+            v[4 * q + 1] += f[q].y;
+            v[4 * q + 2] += f[q].z;
+            v[4 * q + 3] += f[q].w;
+          }
+          if (more) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) f[q] = g[q];
+          }
         }
-      }
+        if (!row_ok) continue;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] *= ep.alpha;
+        for (int j = 0; j < 32; ++j) v[j] *= ep.alpha;
+      } else {
+        tmem_ld_wait();
+        if (!row_ok) continue;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * ep.alpha;
+      }
     }
     const bool full_chunk = (col0 + 32 <= N);
     if (full_chunk) {
@@ -775,7 +792,6 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tma_a, const C
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* epoch_slot = tmem_slot + 2;
   uint32_t* need_slot = tmem_slot + 3;  // fused reduce: peers must have started a launch with at least this epoch
-  volatile uint32_t* last_slot = tmem_slot + 4;  // split-K, per accumulator buffer: this CTA finishes the tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -990,46 +1006,61 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tma_a, const C
       const bool row_ok = row < M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BN;
       if constexpr (SPLITK) {
-        // pass 1: this split's partial tile -> workspace (fp32, a 128-byte run per lane and chunk)
-        float* ws_tile = ep.splitk_ws + static_cast<size_t>(tile) * splits * kBM * BN;
-        float* mine = ws_tile + (static_cast<size_t>(unit / num_tiles) * kBM + quad * 32 + lane) * BN;
+        // Splits 0 .. splits-2 store their fp32 partial tile; the LAST split of a tile
+        // keeps its own part in TMEM, waits for the others (they have lower unit
+        // numbers, so they were started earlier and never wait themselves), adds them
+        // in split order and runs the epilogue.  Workspace layout per (tile, split):
+        // [chunk of 32 columns][quad][q][lane] float4, i.e. every store or load of a
+        // warp is one 512-byte run.
+        const int sp = unit / num_tiles;
+        float4* ws_tile = reinterpret_cast<float4*>(ep.splitk_ws + static_cast<size_t>(tile) * (splits - 1) * kBM * BN);
+        unsigned* cnt = ep.splitk_counters + tile;
+        const unsigned all_in = 8u * static_cast<unsigned>(splits - 1);
+        if (sp < splits - 1) {
+          float4* mine = ws_tile + static_cast<size_t>(sp) * (kBM * BN / 4) + quad * 256 + lane;
 #pragma unroll 1
-        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c * 32, r);
-          tmem_ld_wait();
-          float4* dst = reinterpret_cast<float4*>(mine + c * 32);
+          for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c * 32, r);
+            tmem_ld_wait();
+            float4* dst = mine + c * 1024;
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            __stcg(dst + q, make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
+            for (int q = 0; q < 8; ++q)
+              __stcg(dst + q * 32, make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(&acc_empty[buf]);
+            __threadfence();
+            atomicAdd(cnt, 1u);
+          }
+          continue;
         }
+        bool ok = true;
+        if (lane == 0) {
+          const long long t0 = clock64();
+          while (ld_acquire_gpu(cnt) < all_in) {
+            if (*abort_flag != 0 || clock64() - t0 > kWaitBudgetCycles) {
+              if (*abort_flag == 0) report_status(status, kMbarTimeout, 18);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+          }
+        }
+        if (!__all_sync(0xffffffffu, ok)) break;
+        epilogue_columns<BN, false>(ep, fc, t_row, row, row_ok, n0, half, N,
+                                    reinterpret_cast<const float*>(ws_tile + quad * 256 + lane),
+                                    reinterpret_cast<uint4*>(smem + L::kTotal) + (warp - 2) * 256, lane, M);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(&acc_empty[buf]);
-          mbar_arrive(&tile_done[buf]);
+          // the last of the eight warps to finish reading re-arms the counter
+          if (atomicAdd(cnt, 1u) == all_in + 7u) atomicExch(cnt, 0u);
         }
-        // one thread counts this CTA in; the last split of the tile to arrive finishes it
-        if (warp == 2 && lane == 0) {
-          if (mbar_wait(&tile_done[buf], acc_phase, abort_flag, status, 18)) {
-            __threadfence();
-            const unsigned seen = atomicAdd(&ep.splitk_counters[tile], 1u);
-            const bool last = seen == static_cast<unsigned>(splits) - 1;
-            if (last) ep.splitk_counters[tile] = 0;
-            __threadfence();
-            last_slot[buf] = last ? 1u : 0u;
-          } else {
-            last_slot[buf] = 0u;
-          }
-          mbar_arrive(&decided[buf]);
-        }
-        bool go = true;
-        if (lane == 0) go = mbar_wait(&decided[buf], acc_phase, abort_flag, status, 19);
-        if (!__all_sync(0xffffffffu, go)) break;
-        if (last_slot[buf] != 0u)
-          epilogue_columns<BN, false>(ep, fc, t_row, row, row_ok, n0, half, N,
-                                      ws_tile + static_cast<size_t>(quad * 32 + lane) * BN);
         continue;
       }
       if (!reducing) {
@@ -1141,13 +1172,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 // per CTA instead of 48 KB for the same 128 x 256 of output, which is what
 // bounds the single-CTA kernel.  No multicast load: the halves differ.
 //
-//   warp 0      TMA producer (both CTAs, own barriers)
-//   warp 1      even CTA: MMA issuer for the pair; odd CTA: relay that forwards
-//               "my stage is full" to the even CTA's peer_full barrier
+//   warp 0      TMA producer (both CTAs): waits on its own CTA's empty barrier,
+//               counts the bytes of its loads on the EVEN CTA's full barrier
+//   warp 1      even CTA only: MMA issuer for the pair
 //   warps 2..9  epilogue (both CTAs, own 128 rows of D)
-// The issuer commits to the even CTA's empty / acc_full barriers; that CTA's
-// producer / first epilogue warp forward those signals to the odd CTA, whose
-// epilogue warps in turn arrive on the even CTA's acc_empty barriers.
+// No thread relays a signal between the CTAs: the issuer's tcgen05.commit arrives
+// on the empty / acc_full barrier of both CTAs at once, the odd CTA's loads
+// complete on the even CTA's full barrier (its producer expects the bytes of
+// both), and the odd CTA's epilogue warps arrive on the even CTA's acc_empty
+// barriers once per tile.
 // Optional cycle accounting of the roles of pair 0 (built only with
 // -DNMB_GEMM_PROF; the counters go to the buffer passed as `aux_in` of a plain
 // epilogue): where each role's time goes between waiting and working.
@@ -1168,8 +1201,8 @@ struct GemmPairSmem {
   static constexpr int kBBytes = 128 * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarOffset = kStages * kStageBytes;
-  // full, empty, peer_full [kStages]; acc_full[2], acc_empty[2]; tmem slot, abort
-  static constexpr int kTotal = kBarOffset + (3 * kStages + 4) * 8 + 16;
+  // full, empty [kStages]; acc_full[2], acc_empty[2]; tmem slot, abort
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16;
 };
 
 template <bool A_MN, bool B_MN>
@@ -1184,8 +1217,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
   uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* peer_full = empty_bar + STAGES;
-  uint64_t* acc_full = peer_full + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -1206,7 +1238,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
-      mbar_init(&peer_full[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
@@ -1233,34 +1264,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int fills = 0;
+      // Both CTAs' loads count their bytes on the even CTA's full barrier.
+      const uint32_t full0 = cluster_addr(&full_bar[0], 0);
       GP_DECL
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
         const int m0 = (tile % tiles_m) * 256 + static_cast<int>(cta) * 128;
         const int nb0 = (tile / tiles_m) * BN + static_cast<int>(cta) * 128;
-        for (int kb = 0; kb < num_kb; ++kb, ++fills) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          // released in both CTAs at once by the issuer's commit
           if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1, abort_flag, status, 11)) {
             ok = false;
             break;
           }
-          // The issuer commits to the even CTA's barrier only; pass a real
-          // release (not the free first lap of the ring) on to the odd CTA.
           GP_LAP(0);  // waited for an empty stage
-          if (leader && fills >= STAGES) mbar_arrive_cluster(cluster_addr(&empty_bar[stage], 1));
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
-          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          const uint32_t fb = full0 + stage * 8;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * L::kStageBytes);
           if (!A_MN) {
-            tma_load_2d(sa, &tma_a, &full_bar[stage], kb * kBK, m0);
+            tma_load_2d_pair(sa, &tma_a, fb, kb * kBK, m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tma_load_2d(sa + c * 8192, &tma_a, &full_bar[stage], m0 + c * 64, kb * kBK);
+            for (int c = 0; c < 2; ++c) tma_load_2d_pair(sa + c * 8192, &tma_a, fb, m0 + c * 64, kb * kBK);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * kBK, nb0);
+            tma_load_2d_pair(sb, &tma_b, fb, kb * kBK, nb0);
           } else {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) tma_load_2d(sb + c * 8192, &tma_b, &full_bar[stage], nb0 + c * 64, kb * kBK);
+            for (int c = 0; c < 2; ++c) tma_load_2d_pair(sb + c * 8192, &tma_b, fb, nb0 + c * 64, kb * kBK);
           }
           GP_LAP(1);  // issued the loads
           if (++stage == STAGES) {
@@ -1288,16 +1319,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         GP_LAP(0);  // waited for a free accumulator
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, 13)) {
+          if (!mbar_wait_cluster(&full_bar[stage], phase, abort_flag, status, 13)) {
             ok = false;
             break;
           }
-          GP_LAP(1);  // waited for this CTA's loads
-          if (!mbar_wait_cluster(&peer_full[stage], phase, abort_flag, status, 14)) {
-            ok = false;
-            break;
-          }
-          GP_LAP(2);  // waited for the odd CTA's loads
+          GP_LAP(1);  // waited for both CTAs' loads
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
           const uint32_t sb = sa + L::kABytes;
@@ -1309,40 +1335,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                      : make_smem_desc(sb + k * 32, 16, 1024);
             tc_mma_bf16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          // the stage may be refilled once these MMAs have read it (the even
-          // CTA's producer forwards the release to the odd CTA)
-          tc_commit_pair(smem_u32(&empty_bar[stage]));
+          // the stage may be refilled in both CTAs once these MMAs have read it
+          tc_commit_pair_both(&empty_bar[stage]);
           GP_LAP(3);  // issued MMAs + commit
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) tc_commit_pair(smem_u32(&acc_full[buf]));  // forwarded to the odd CTA by epilogue warp 2
+        if (ok) tc_commit_pair_both(&acc_full[buf]);
       }
       GP_STORE(8);
-    } else if (lane == 0) {
-      // ------------------------------------------ relay of the odd CTA's loads --
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      GP_DECL
-      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, status, 15)) {
-            ok = false;
-            break;
-          }
-          GP_LAP(0);  // waited for the odd CTA's loads
-          mbar_arrive_cluster(cluster_addr(&peer_full[stage], 0));
-          GP_LAP(1);  // forwarded
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-      }
-      GP_STORE(12);
     }
   } else {
     // ------------------------------------------------------------ epilogue --
@@ -1355,7 +1358,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int m0 = (tile % tiles_m) * 256 + static_cast<int>(cta) * 128;
       const int n0 = (tile / tiles_m) * BN;
       if (!mbar_wait_cluster(&acc_full[buf], acc_phase, abort_flag, status, 16)) break;
-      if (leader && warp == 2 && lane == 0) mbar_arrive_cluster(cluster_addr(&acc_full[buf], 1));
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < M;
@@ -1514,17 +1516,28 @@ static long long g_splitk_ws_bytes[kMaxDevices] = {0};
 static unsigned* g_splitk_counters[kMaxDevices] = {nullptr};
 static int g_splitk_n_counters[kMaxDevices] = {0};
 
-// How many ways to cut K so that tiles * splits comes close to filling the SMs:
-// only for GEMMs whose tiles fill less than half of the machine and whose K is
-// long enough that a split still has >= 8 k-blocks to amortise its epilogue.
+// How many ways to cut K.  Cost model in units of one k-block of MMA time: a unit
+// (tile x split) costs its k-blocks plus a fixed ~6 for the pipeline fill and the
+// epilogue (+2 when partial tiles are exchanged), and the kernel takes as many
+// rounds as the units need on the SMs.  A split is taken when the model says at
+// least 10 % less than the unsplit kernel, each piece keeping >= 8 k-blocks.
 static int choose_splits(int tiles, int num_kb, int dev) {
   if (dev < 0 || dev >= kMaxDevices || g_splitk_ws[dev] == nullptr) return 1;
-  if (tiles * 2 > sm_count() || num_kb < 16 || tiles > g_splitk_n_counters[dev]) return 1;
-  int s = sm_count() / tiles;
-  if (s > num_kb / 8) s = num_kb / 8;
-  if (s > 8) s = 8;
-  while (s > 1 && static_cast<long long>(tiles) * s * kBM * 256 * 4 > g_splitk_ws_bytes[dev]) --s;
-  return s < 2 ? 1 : s;
+  if (num_kb < 16 || tiles > g_splitk_n_counters[dev]) return 1;
+  const int sms = sm_count();
+  const long long base = static_cast<long long>((tiles + sms - 1) / sms) * (num_kb + 6);
+  int best = 1;
+  long long best_cost = base;
+  for (int s = 2; s <= 8 && num_kb / s >= 8; ++s) {
+    if (static_cast<long long>(tiles) * (s - 1) * kBM * 256 * 4 > g_splitk_ws_bytes[dev]) break;
+    const long long rounds = (static_cast<long long>(tiles) * s + sms - 1) / sms;
+    const long long cost = rounds * ((num_kb + s - 1) / s + 8);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best_cost * 10 <= base * 9 ? best : 1;
 }
 
 template <bool A_MN, bool B_MN>

@@ -99,6 +99,26 @@ def bench_attn(args) -> None:
     _report(f"attention fwd b{b} s{s} h{h} d{d}", _timed(lambda: attn_fwd(q, [k], [v], scale), args.iters), fwd_flops)
     _report("attention bwd (prep + main + dq store)", _timed(lambda: attn_bwd(q, [k], [v], out, g, lse, scale), args.iters),
             2.5 * fwd_flops)
+    if args.library:
+        _bench_library_attention(args, qkv, g, fwd_flops)
+
+
+def _bench_library_attention(args, qkv, g, fwd_flops) -> None:
+    """The same workload through the flash-attn package, as a yardstick only (it is not
+    on any path of this framework)."""
+    try:
+        from flash_attn import flash_attn_func
+    except Exception as exc:  # not installed: say so and carry on
+        print(f"flash-attn not importable: {exc}", flush=True)
+        return
+    b, s, h, d = args.batch, args.seq, args.heads, args.dim
+    q, k, v = (t.contiguous().requires_grad_(True) for t in qkv.view(b, s, 3, h, d).unbind(2))
+    scale = 1.0 / math.sqrt(d)
+    _report("flash-attn (library) fwd", _timed(lambda: flash_attn_func(q, k, v, softmax_scale=scale, causal=True), args.iters),
+            fwd_flops)
+    out = flash_attn_func(q, k, v, softmax_scale=scale, causal=True)
+    _report("flash-attn (library) bwd", _timed(lambda: torch.autograd.grad(out, (q, k, v), g, retain_graph=True), args.iters),
+            2.5 * fwd_flops)
 
 
 def bench_norm(args) -> None:
@@ -151,6 +171,7 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--variants", action="store_true")
     ap.add_argument("--epilogues", action="store_true", help="gemm: also time the rotary / SwiGLU epilogue GEMMs")
+    ap.add_argument("--library", action="store_true", help="attn: also time the flash-attn package on the same workload")
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16)

@@ -6,6 +6,8 @@ import math
 import pytest
 import torch
 
+from tests._numerics import assert_rel_fro
+
 pytestmark = pytest.mark.gpu
 
 
@@ -47,6 +49,7 @@ def test_flash_fwd_bwd(b, s, hq, hkv, d):
     rv = ref_in[..., (hq + hkv) * d:].view(b, s, hkv, d)
     ref = _ref(rq, rk, rv, scale)
     assert (out.float() - ref).abs().max().item() < 2e-2
+    assert_rel_fro(out, ref, 1e-2, "attention forward")
     g = torch.randn_like(ref)
     ref.backward(g)
     out.backward(g.to(torch.bfloat16))
@@ -54,6 +57,7 @@ def test_flash_fwd_bwd(b, s, hq, hkv, d):
     native.check_status()
     err = (qkv.grad.float() - ref_in.grad).abs().max().item()
     assert err < 5e-2 * max(1.0, ref_in.grad.abs().max().item()), err
+    assert_rel_fro(qkv.grad, ref_in.grad, 2e-2, "attention backward")
 
 
 @pytest.mark.parametrize("b,s,hq,hkv,d", [(2, 256, 4, 4, 64), (1, 200, 4, 2, 64), (1, 256, 2, 2, 128)])

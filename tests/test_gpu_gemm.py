@@ -4,6 +4,8 @@ from __future__ import annotations
 import pytest
 import torch
 
+from tests._numerics import assert_rel_fro
+
 pytestmark = pytest.mark.gpu
 
 
@@ -33,6 +35,7 @@ def test_gemm_layouts(a_mn, b_mn, m, n, k):
     err = (out.float() - ref).abs().max().item()
     tol = 2e-2 * ref.abs().max().item() + 1e-3
     assert err <= tol, f"max err {err} > {tol}"
+    assert_rel_fro(out, ref, 5e-3, "gemm")  # bf16 rounding of the output is ~2e-3
 
 
 def test_gemm_epilogues():
@@ -48,12 +51,15 @@ def test_gemm_epilogues():
     out = gemm_bf16(a, b, bias=bias, residual=res)
     want = ref + bias.float() + res.float()
     assert (out.float() - want).abs().max().item() < 5e-2
+    assert_rel_fro(out, want, 5e-3, "bias + residual epilogue")
 
     aux = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
     g = gemm_bf16(a, b, bias=bias, mode=EPI_GELU, aux_out=aux)
     h = ref + bias.float()
     assert (aux.float() - h).abs().max().item() < 5e-2
     assert (g.float() - torch.nn.functional.gelu(aux.float())).abs().max().item() < 2e-2
+    assert_rel_fro(aux, h, 5e-3, "pre-activation")
+    assert_rel_fro(g, torch.nn.functional.gelu(h), 1e-2, "GELU epilogue")
 
     dg = gemm_bf16(a, b, mode=EPI_DGELU, aux_in=aux)
     x = aux.float().requires_grad_(True)
