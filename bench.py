@@ -274,6 +274,8 @@ def measure(args, spec: dict, steps: int, warmup: int) -> dict:
     ms_e2e, _, _ = timed(lambda i: runner.step_host(pool[i % 4]), steps)
 
     # ---- the reference's benchmark step: no optimizer update ----
+    runner.prepare_no_optimizer(ids_dev[0])   # set-up (eager steps + capture), as above
+    barrier()
     for i in range(max(warmup, 3)):
         runner.step_no_optimizer(ids_dev[i % 4])
     ms_nopt, _, _ = timed(lambda i: runner.step_no_optimizer(ids_dev[i % 4]), steps)
@@ -497,6 +499,13 @@ class B200Runner:
             self.trainer.step(ids_dev)
         self.graphed = self.trainer.graphed
 
+    def prepare_no_optimizer(self, ids_dev) -> None:
+        settled = getattr(self.trainer, "graph_settled", None)
+        for _ in range(8):
+            if settled is None or self.args.no_graph or settled(False):
+                break
+            self.trainer.forward_backward(ids_dev)
+
     def step_host(self, ids_pinned):
         loss = self.trainer.step(ids_pinned)
         return None if loss is None else loss.item()
@@ -612,6 +621,9 @@ class ReferenceRunner:
         pass
 
     def prepare(self, ids_dev) -> None:
+        pass
+
+    def prepare_no_optimizer(self, ids_dev) -> None:
         pass
 
     def close(self) -> None:

@@ -31,7 +31,7 @@
 namespace nmb {
 
 constexpr int kMaxChunks = 8;
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;  // 8 softmax warps, TMA warp, MMA warp
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 of the growth tolerated before O is rescaled
 
@@ -45,11 +45,37 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// 64-thread barrier of the two warps that share TMEM lane quadrant `quad`
+// (barriers 1..4; 0 is __syncthreads).  Immediate ids keep the kernel's barrier
+// count at five.
+__device__ __forceinline__ void quad_pair_sync(int quad) {
+  switch (quad) {
+    case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+  }
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+// Cycle accounting of the forward kernel (profiling builds, -DNMB_ATTN_PROF): the
+// first softmax thread and the MMA thread of CTA (0, 0, 0) add up where their time
+// goes; nmb_attn_fwd_prof_read() copies the counters out.
+#ifdef NMB_ATTN_PROF
+__device__ long long g_attn_fwd_prof[16];
+#define FP_DECL(on) const bool fp_on = (on) && blockIdx.x == 0; long long fp_t = clock64(); long long fp_acc[6] = {0, 0, 0, 0, 0, 0};
+#define FP_LAP(k) do { if (fp_on) { const long long t = clock64(); fp_acc[k] += t - fp_t; fp_t = t; } } while (0)
+#define FP_STORE(base) do { if (fp_on) for (int k = 0; k < 6; ++k) g_attn_fwd_prof[(base) + k] = fp_acc[k]; } while (0)
+#else
+#define FP_DECL(on)
+#define FP_LAP(k)
+#define FP_STORE(base)
+#endif
 
 struct AttnFwdParams {
   CUtensorMap q_map;
@@ -76,7 +102,8 @@ struct AttnFwdSmem {
   static constexpr int kP = kV + 2 * kTile;      // 128 x 128 bf16
   static constexpr int kBar = kP + 32768;
   static constexpr int kNumBars = 9;
-  static constexpr int kTotal = kBar + kNumBars * 8 + 16;
+  static constexpr int kXch = kBar + kNumBars * 8 + 16;  // tile maxima of the two threads of a row, bf16 [2][128]
+  static constexpr int kTotal = kXch + 512;
 };
 
 template <int HD>
@@ -98,10 +125,16 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_q_tiles = gridDim.x;
-  const int qt = n_q_tiles - 1 - blockIdx.x;  // longest tiles first
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
+  // One-dimensional grid, longest work first across the WHOLE grid: block i takes
+  // query tile n_q_tiles - 1 - i / (heads * batch), so the causal tiles with the
+  // most key tiles start first on every SM and the short ones fill the tail
+  // (with (tile, head, batch) as a 3-D grid the tile index ran fastest, long and
+  // short CTAs were interleaved and the last long ones started late).
+  const int n_q_tiles = (p.Sq + 127) / 128;
+  const int n_hb = p.Hq * p.B;
+  const int qt = n_q_tiles - 1 - static_cast<int>(blockIdx.x) / n_hb;
+  const int h = (static_cast<int>(blockIdx.x) % n_hb) % p.Hq;
+  const int b = (static_cast<int>(blockIdx.x) % n_hb) / p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qt * 128;
   const int skv_total = p.chunk_len * p.n_chunks;
@@ -124,13 +157,13 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 128);
-    mbar_init(p_full, 128);
+    mbar_init(s_empty, 256);
+    mbar_init(p_full, 256);
     mbar_init(o_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -139,7 +172,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------ producer --
     if (lane == 0) {
       tma_prefetch_desc(&p.q_map);
@@ -162,7 +195,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------- MMA issuer --
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
@@ -179,6 +212,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         }
         tc_commit(s_full);
       };
+      FP_DECL(true)
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status, 22) &&
                 mbar_wait(&kv_full[0], 0, abort_flag, p.status, 23);
       if (ok) {
@@ -194,13 +228,16 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
             ok = false;
             break;
           }
+          FP_LAP(0);  // waited for K/V of the next tile and for S to be read
           tc_fence_after();
           issue_qk(j + 1);
+          FP_LAP(1);  // issued QK^T
         }
         if (!mbar_wait(p_full, j & 1, abort_flag, p.status, 26)) {
           ok = false;
           break;
         }
+        FP_LAP(2);  // waited for P
         tc_fence_after();
         const uint32_t sV = smem_u32(smem + L::kV + (j & 1) * L::kTile);
 #pragma unroll
@@ -211,23 +248,36 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         }
         tc_commit(o_full);
         tc_commit(&kv_empty[j & 1]);
+        FP_LAP(3);  // issued PV
       }
+      FP_STORE(8);
     }
   } else {
     // ------------------------------------------------- softmax + epilogue --
-    const int r = threadIdx.x;  // query row in the tile == TMEM lane
-    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    // Eight warps, two threads per query row: warp w owns TMEM lanes (rows)
+    // 32 * (w & 3) .. + 31 and columns 64 * (w >> 2) .. + 63 of S, and the same
+    // half of O's columns.  The two threads of a row agree on the tile maximum
+    // through shared memory (each rounds its own maximum UP to bf16 first, so
+    // both compute the same value from the same pair) under a 64-thread named
+    // barrier of their quad, and add their row sums at the end.
+    const int quad = warp & 3;
+    const int half = warp >> 2;
+    const int r = quad * 32 + lane;  // query row in the tile == TMEM lane
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    __nv_bfloat16* xch = reinterpret_cast<__nv_bfloat16*>(smem + L::kXch);  // [2 halves][128 rows]
     const int q_row = q0 + r;
     const int q_pos = p.q_pos0 + q_row;
     const float sl2 = p.scale * kLog2e;
     float m_run = -INFINITY;
     float l_run = 0.f;
     bool ok = true;
+    FP_DECL(threadIdx.x == 0)
     for (int j = 0; j < n_kv; ++j) {
       if (!mbar_wait(s_full, j & 1, abort_flag, p.status, 27)) {
         ok = false;
         break;
       }
+      FP_LAP(0);  // waited for S
       tc_fence_after();
       const int kv0 = j * 128;
       // A tile is "full" when every key of it is visible to every query row of
@@ -235,25 +285,23 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       const bool tile_full = (kv0 + 127 <= p.q_pos0 + q0) && (kv0 + 128 <= skv_total);
       int limit = q_pos - kv0;                       // columns <= limit are visible
       if (skv_total - 1 - kv0 < limit) limit = skv_total - 1 - kv0;
-      // pass 1: tile maximum
+      // pass 1: maximum of this thread's 64 columns
       float mx = -INFINITY;
       if (tile_full) {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t sr[32];
-          tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
-          tmem_ld_wait();
-          float m0 = __uint_as_float(sr[0]), m1 = __uint_as_float(sr[1]);
+        uint32_t sa[32], sb[32];
+        tmem_ld_32x32(t_lane + kSCol + half * 64, sa);
+        tmem_ld_32x32(t_lane + kSCol + half * 64 + 32, sb);
+        tmem_ld_wait();
+        float m0 = __uint_as_float(sa[0]), m1 = __uint_as_float(sb[0]);
 #pragma unroll
-          for (int jj = 2; jj < 32; jj += 2) {
-            m0 = fmaxf(m0, __uint_as_float(sr[jj]));
-            m1 = fmaxf(m1, __uint_as_float(sr[jj + 1]));
-          }
-          mx = fmaxf(mx, fmaxf(m0, m1));
+        for (int jj = 1; jj < 32; ++jj) {
+          m0 = fmaxf(m0, __uint_as_float(sa[jj]));
+          m1 = fmaxf(m1, __uint_as_float(sb[jj]));
         }
+        mx = fmaxf(m0, m1);
       } else {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = half * 2; c < half * 2 + 2; ++c) {
           uint32_t sr[32];
           tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
           tmem_ld_wait();
@@ -262,6 +310,15 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
             if (c * 32 + jj <= limit) mx = fmaxf(mx, __uint_as_float(sr[jj]));
         }
       }
+      FP_LAP(1);  // pass 1
+      {
+        const __nv_bfloat16 mine = __float2bfloat16_ru(mx);
+        xch[half * 128 + r] = mine;
+        quad_pair_sync(quad);
+        mx = fmaxf(__bfloat162float(mine), __bfloat162float(xch[(half ^ 1) * 128 + r]));
+        quad_pair_sync(quad);  // both have read before either writes the next tile's value
+      }
+      FP_LAP(2);  // exchanged the maximum
       // Lazy rescaling: the reference maximum only moves when the tile maximum
       // exceeds it by more than 2^8 in the exponent domain, so most tiles need
       // no pass over O; the final division by l makes the result exact.
@@ -269,14 +326,14 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       if (mx > m_run + kRescaleThreshold / sl2) m_new = mx;
       const float alpha = (m_new == m_run) ? 1.f : ((m_run == -INFINITY) ? 0.f : fast_exp2((m_run - m_new) * sl2));
       const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new * sl2;
-      // pass 2: probabilities
-      uint32_t pk[64];
+      // pass 2: probabilities of this thread's 64 columns
+      uint32_t pk[32];
       float rowsum = 0.f;
       if (tile_full) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t sr[32];
-          tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+          tmem_ld_32x32(t_lane + kSCol + half * 64 + c * 32, sr);
           tmem_ld_wait();
           float r0 = 0.f, r1 = 0.f;
 #pragma unroll
@@ -291,14 +348,15 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t sr[32];
-          tmem_ld_32x32(t_lane + kSCol + c * 32, sr);
+          tmem_ld_32x32(t_lane + kSCol + half * 64 + c * 32, sr);
           tmem_ld_wait();
+          const int col0 = half * 64 + c * 32;
 #pragma unroll
           for (int jj = 0; jj < 32; jj += 2) {
-            const float p0 = (c * 32 + jj <= limit) ? fast_exp2(fmaf(__uint_as_float(sr[jj]), sl2, neg_m)) : 0.f;
-            const float p1 = (c * 32 + jj + 1 <= limit) ? fast_exp2(fmaf(__uint_as_float(sr[jj + 1]), sl2, neg_m)) : 0.f;
+            const float p0 = (col0 + jj <= limit) ? fast_exp2(fmaf(__uint_as_float(sr[jj]), sl2, neg_m)) : 0.f;
+            const float p1 = (col0 + jj + 1 <= limit) ? fast_exp2(fmaf(__uint_as_float(sr[jj + 1]), sl2, neg_m)) : 0.f;
             rowsum += p0 + p1;
             pk[c * 16 + jj / 2] = pack_bf16x2(p0, p1);
           }
@@ -306,6 +364,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       }
       tc_fence_before();
       mbar_arrive(s_empty);
+      FP_LAP(3);  // pass 2
       l_run = l_run * alpha + rowsum;
       m_run = m_new;
       if (j > 0) {
@@ -316,7 +375,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
+          for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
             uint32_t orr[32];
             tmem_ld_32x32(t_lane + kOCol + c * 32, orr);
             tmem_ld_wait();
@@ -327,24 +386,33 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
           tmem_st_wait();
         }
       }
-      // P -> shared memory, K-major, 128-byte swizzle (two 64-column slabs).
-      uint8_t* sp = smem + L::kP;
+      FP_LAP(4);  // waited for the previous PV, rescaled O if needed
+      // P -> shared memory, K-major, 128-byte swizzle: this thread's 64 columns
+      // are one row of slab `half`.
+      uint8_t* sp = smem + L::kP + half * 16384;
 #pragma unroll
-      for (int c16 = 0; c16 < 16; ++c16) {
+      for (int c16 = 0; c16 < 8; ++c16) {
         uint4 u = make_uint4(pk[c16 * 4], pk[c16 * 4 + 1], pk[c16 * 4 + 2], pk[c16 * 4 + 3]);
-        *reinterpret_cast<uint4*>(sp + (c16 >> 3) * 16384 + swz128_offset(r, c16 & 7)) = u;
+        *reinterpret_cast<uint4*>(sp + swz128_offset(r, c16)) = u;
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_full);
+      FP_LAP(5);  // stored P
     }
+    FP_STORE(0);
     if (ok && mbar_wait(o_full, (n_kv - 1) & 1, abort_flag, p.status, 29)) {
       tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      // every MMA has completed: the P buffer is free and carries the row sums
+      float* lx = reinterpret_cast<float*>(smem + L::kP);
+      lx[half * 128 + r] = l_run;
+      quad_pair_sync(quad);
+      const float l_tot = l_run + lx[(half ^ 1) * 128 + r];
+      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
       __nv_bfloat16* orow = p.o + b * p.o_stride_b + static_cast<long long>(q_row) * p.o_stride_s +
                             h * p.o_stride_h;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); ++c) {
         uint32_t orr[32];
         tmem_ld_32x32(t_lane + kOCol + c * 32, orr);
         tmem_ld_wait();
@@ -361,8 +429,8 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
           }
         }
       }
-      if (q_row < p.Sq)
-        p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + q_row] = m_run * p.scale + logf(l_run);
+      if (half == 0 && q_row < p.Sq)
+        p.lse[(static_cast<long long>(b) * p.Hq + h) * p.Sq + q_row] = m_run * p.scale + logf(l_tot);
     }
   }
 
@@ -371,7 +439,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -401,7 +469,7 @@ struct AttnBwdParams {
 };
 
 #ifdef NMB_ATTN_PROF
-#define NMB_PROF_DECL long long pt0 = 0, pacc[6] = {0, 0, 0, 0, 0, 0}; const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+#define NMB_PROF_DECL long long pt0 = 0, pacc[6] = {0, 0, 0, 0, 0, 0}; const bool prof_on = blockIdx.x == 0 && threadIdx.x == 0;
 #define NMB_PROF_START() do { if (prof_on) pt0 = clock64(); } while (0)
 #define NMB_PROF_LAP(k) do { if (prof_on) { const long long t = clock64(); pacc[k] += t - pt0; pt0 = t; } } while (0)
 #define NMB_PROF_STORE() do { if (prof_on) { for (int k = 0; k < 6; ++k) p.prof[k] = pacc[k]; p.prof[6] = n_iter; } } while (0)
@@ -460,9 +528,12 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int kvt = blockIdx.x;
-  const int hk = blockIdx.y;
-  const int b = blockIdx.z;
+  // One-dimensional grid, longest work first: the lowest key tiles are visible to
+  // the most query tiles, so all (head, batch) pairs of key tile 0 come first.
+  const int n_hb = p.Hkv * p.B;
+  const int kvt = static_cast<int>(blockIdx.x) / n_hb;
+  const int hk = (static_cast<int>(blockIdx.x) % n_hb) % p.Hkv;
+  const int b = (static_cast<int>(blockIdx.x) % n_hb) / p.Hkv;
   const int group = p.Hq / p.Hkv;
   const int kv0 = kvt * 128;
   const int chunk = kv0 / p.chunk_len;
@@ -995,6 +1066,12 @@ extern "C" int nmb_attn_configure() {
   return 0;
 }
 
+#ifdef NMB_ATTN_PROF
+extern "C" int nmb_attn_fwd_prof_read(long long* host16) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host16, nmb::g_attn_fwd_prof, 16 * sizeof(long long)));
+}
+#endif
+
 extern "C" int nmb_attn_fwd(const NmbTensor4* q, const NmbTensor4* k_chunks, const NmbTensor4* v_chunks,
                             int n_chunks, int chunk_len, const NmbTensor4* o, float* lse, int B, int Hq,
                             int Hkv, int Sq, int d, int q_pos0, float scale, int* status, void* stream) {
@@ -1020,7 +1097,7 @@ extern "C" int nmb_attn_fwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Sq = Sq;
   p.chunk_len = chunk_len; p.n_chunks = n_chunks;
   p.d = d; p.q_pos0 = q_pos0; p.scale = scale; p.status = status;
-  dim3 grid((Sq + 127) / 128, Hq, B);
+  dim3 grid(((Sq + 127) / 128) * Hq * B);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (d == 64) {
@@ -1075,7 +1152,7 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
 #ifdef NMB_ATTN_PROF
   p.prof = reinterpret_cast<long long*>(delta) - 8;  // profiling builds: the caller over-allocates delta by 8 slots in front
 #endif
-  dim3 grid(n_visible_kv_tiles, Hkv, B);
+  dim3 grid(n_visible_kv_tiles * Hkv * B);
   cudaError_t e;
   if (d == 64) {
     attn_bwd_kernel<64><<<grid, kBwdThreads, AttnBwdSmem<64>::kTotal, s>>>(p);

@@ -169,6 +169,12 @@ class Trainer:
             torch.cuda.synchronize(self.device)
             return None
 
+    def graph_settled(self, with_optimizer: bool) -> bool:
+        """True once that kind of step will not change mode any more: it is captured, its
+        capture was tried and failed, or graphs are not wanted.  A benchmark calls the step
+        until this holds so that no timed region contains a capture."""
+        return (not self._want_graph) or with_optimizer in self._graphs or with_optimizer in self._tried
+
     def reset_graphs(self) -> None:
         """Drop the captured graphs (they are re-captured after the usual eager
         warm-up).  Needed after anything that moves a tensor the graphs address:
