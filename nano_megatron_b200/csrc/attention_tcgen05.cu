@@ -68,6 +68,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // goes; nmb_attn_fwd_prof_read() copies the counters out.
 #ifdef NMB_ATTN_PROF
 __device__ long long g_attn_fwd_prof[16];
+__device__ unsigned long long g_attn_fwd_span[4096][2];  // per CTA: start / end of its life, ns (globaltimer)
+__device__ unsigned long long g_attn_fwd_marks[4096][4];  // per CTA: set-up done, first S, loop end, O written
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 #define FP_DECL(on) const bool fp_on = (on) && blockIdx.x == 0; long long fp_t = clock64(); long long fp_acc[6] = {0, 0, 0, 0, 0, 0};
 #define FP_LAP(k) do { if (fp_on) { const long long t = clock64(); fp_acc[k] += t - fp_t; fp_t = t; } } while (0)
 #define FP_STORE(base) do { if (fp_on) for (int k = 0; k < 6; ++k) g_attn_fwd_prof[(base) + k] = fp_acc[k]; } while (0)
@@ -111,6 +118,9 @@ __global__ void __launch_bounds__(kAttnThreads, HD == 64 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
   using L = AttnFwdSmem<HD>;
   constexpr int NS = L::kSlabs;
+#ifdef NMB_ATTN_PROF
+  if (threadIdx.x == 0 && blockIdx.x < 4096) g_attn_fwd_span[blockIdx.x][0] = global_ns();
+#endif
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
   uint64_t* q_full = &bars[0];
@@ -171,6 +181,9 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef NMB_ATTN_PROF
+  if (threadIdx.x == 0 && blockIdx.x < 4096) g_attn_fwd_marks[blockIdx.x][0] = global_ns();
+#endif
 
   if (warp == 8) {
     // ------------------------------------------------------------ producer --
@@ -278,6 +291,9 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
         break;
       }
       FP_LAP(0);  // waited for S
+#ifdef NMB_ATTN_PROF
+      if (j == 0 && threadIdx.x == 0 && blockIdx.x < 4096) g_attn_fwd_marks[blockIdx.x][1] = global_ns();
+#endif
       tc_fence_after();
       const int kv0 = j * 128;
       // A tile is "full" when every key of it is visible to every query row of
@@ -401,6 +417,9 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
       FP_LAP(5);  // stored P
     }
     FP_STORE(0);
+#ifdef NMB_ATTN_PROF
+    if (threadIdx.x == 0 && blockIdx.x < 4096) g_attn_fwd_marks[blockIdx.x][2] = global_ns();
+#endif
     if (ok && mbar_wait(o_full, (n_kv - 1) & 1, abort_flag, p.status, 29)) {
       tc_fence_after();
       // every MMA has completed: the P buffer is free and carries the row sums
@@ -434,6 +453,9 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
     }
   }
 
+#ifdef NMB_ATTN_PROF
+  if (threadIdx.x == 0 && blockIdx.x < 4096) g_attn_fwd_marks[blockIdx.x][3] = global_ns();
+#endif
   if (*abort_flag != 0) {
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
   }
@@ -443,6 +465,9 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+#ifdef NMB_ATTN_PROF
+  if (threadIdx.x == 0 && blockIdx.x < 4096) g_attn_fwd_span[blockIdx.x][1] = global_ns();
+#endif
 }
 
 // ------------------------------------------------------------------ backward --
@@ -1069,6 +1094,12 @@ extern "C" int nmb_attn_configure() {
 #ifdef NMB_ATTN_PROF
 extern "C" int nmb_attn_fwd_prof_read(long long* host16) {
   return static_cast<int>(cudaMemcpyFromSymbol(host16, nmb::g_attn_fwd_prof, 16 * sizeof(long long)));
+}
+extern "C" int nmb_attn_fwd_marks_read(unsigned long long* host, int n_ctas) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, nmb::g_attn_fwd_marks, sizeof(unsigned long long) * 4 * n_ctas));
+}
+extern "C" int nmb_attn_fwd_span_read(unsigned long long* host, int n_ctas) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, nmb::g_attn_fwd_span, sizeof(unsigned long long) * 2 * n_ctas));
 }
 #endif
 
