@@ -181,6 +181,7 @@ attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_enter();  // the set-up above touches no global memory
 #ifdef NMB_ATTN_PROF
   if (threadIdx.x == 0 && blockIdx.x < 4096) g_attn_fwd_marks[blockIdx.x][0] = global_ns();
 #endif
@@ -604,6 +605,7 @@ attn_bwd_kernel(const __grid_constant__ AttnBwdParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_enter();  // the set-up above touches no global memory
 
   if (warp == 8) {
     // ------------------------------------------------------------ producer --
@@ -930,6 +932,7 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const 
                                      long long o_sb, long long o_ss, long long o_sh, long long do_sb,
                                      long long do_ss, long long do_sh, float* __restrict__ delta,
                                      float* __restrict__ dq_acc, int B, int H, int S, int d) {
+  pdl_enter();
   const int per_row = d >> 3;                       // 8, 12 or 16 threads per row
   const int group = per_row <= 8 ? 8 : 16;          // shuffle width (power of two)
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -996,6 +999,7 @@ __global__ void attn_dq_store_kernel(const float* __restrict__ dq_acc, __nv_bflo
                                      int S, int d, const float2* __restrict__ rope_table,
                                      const long long* __restrict__ rope_pos, __nv_bfloat16* __restrict__ dk,
                                      long long dk_sb, long long dk_ss, long long dk_sh, int Hkv) {
+  pdl_enter();
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long total = static_cast<long long>(B) * S * H * d / 8;
   const int per_row = d / 8;
@@ -1132,11 +1136,10 @@ extern "C" int nmb_attn_fwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (d == 64) {
-    attn_fwd_kernel<64><<<grid, kAttnThreads, AttnFwdSmem<64>::kTotal, s>>>(p);
+    e = launch_pdl(attn_fwd_kernel<64>, grid, dim3(kAttnThreads), AttnFwdSmem<64>::kTotal, s, p);
   } else {
-    attn_fwd_kernel<128><<<grid, kAttnThreads, AttnFwdSmem<128>::kTotal, s>>>(p);
+    e = launch_pdl(attn_fwd_kernel<128>, grid, dim3(kAttnThreads), AttnFwdSmem<128>::kTotal, s, p);
   }
-  e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + e;
 }
 
@@ -1156,9 +1159,9 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
     const long long rows = static_cast<long long>(B) * Sq * Hq;
     const int threads = 256;
     const long long blocks = (rows * (d <= 64 ? 8 : 16) + threads - 1) / threads;
-    attn_bwd_prep_kernel<<<static_cast<unsigned>(blocks), threads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(o->ptr), static_cast<const __nv_bfloat16*>(dout->ptr), o->stride_b,
-        o->stride_s, o->stride_h, dout->stride_b, dout->stride_s, dout->stride_h, delta, dq_acc, B, Hq, Sq, d);
+    launch_pdl(attn_bwd_prep_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0, s,
+               static_cast<const __nv_bfloat16*>(o->ptr), static_cast<const __nv_bfloat16*>(dout->ptr), o->stride_b,
+               o->stride_s, o->stride_h, dout->stride_b, dout->stride_s, dout->stride_h, delta, dq_acc, B, Hq, Sq, d);
   }
   AttnBwdParams p;
   if (make_attn_map(&p.q_map, q->ptr, d, Sq, Hq, B, q->stride_s, q->stride_h, q->stride_b)) return 101;
@@ -1186,11 +1189,10 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
   dim3 grid(n_visible_kv_tiles * Hkv * B);
   cudaError_t e;
   if (d == 64) {
-    attn_bwd_kernel<64><<<grid, kBwdThreads, AttnBwdSmem<64>::kTotal, s>>>(p);
+    e = launch_pdl(attn_bwd_kernel<64>, grid, dim3(kBwdThreads), AttnBwdSmem<64>::kTotal, s, p);
   } else {
-    attn_bwd_kernel<128><<<grid, kBwdThreads, AttnBwdSmem<128>::kTotal, s>>>(p);
+    e = launch_pdl(attn_bwd_kernel<128>, grid, dim3(kBwdThreads), AttnBwdSmem<128>::kTotal, s, p);
   }
-  e = cudaGetLastError();
   if (e != cudaSuccess) return 400 + e;
   {
     // dk is un-rotated in place when the whole key sequence is one local chunk of the
@@ -1200,11 +1202,11 @@ extern "C" int nmb_attn_bwd(const NmbTensor4* q, const NmbTensor4* k_chunks, con
     long long octets = static_cast<long long>(B) * Sq * Hq * d / 8;
     if (unrope_k) octets += static_cast<long long>(B) * Sq * Hkv * d / 8;
     const int threads = 256;
-    attn_dq_store_kernel<<<static_cast<unsigned>((octets + threads - 1) / threads), threads, 0, s>>>(
-        dq_acc, static_cast<__nv_bfloat16*>(dq->ptr), dq->stride_b, dq->stride_s, dq->stride_h, B, Hq, Sq, d,
-        static_cast<const float2*>(rope_table), rope_pos, unrope_k ? static_cast<__nv_bfloat16*>(dk_chunks[0].ptr) : nullptr,
-        dk_chunks[0].stride_b, dk_chunks[0].stride_s, dk_chunks[0].stride_h, Hkv);
+    e = launch_pdl(attn_dq_store_kernel, dim3(static_cast<unsigned>((octets + threads - 1) / threads)), dim3(threads), 0,
+                   s, static_cast<const float*>(dq_acc), static_cast<__nv_bfloat16*>(dq->ptr), dq->stride_b, dq->stride_s,
+                   dq->stride_h, B, Hq, Sq, d, static_cast<const float2*>(rope_table), rope_pos,
+                   unrope_k ? static_cast<__nv_bfloat16*>(dk_chunks[0].ptr) : static_cast<__nv_bfloat16*>(nullptr),
+                   dk_chunks[0].stride_b, dk_chunks[0].stride_s, dk_chunks[0].stride_h, Hkv);
   }
-  e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 500 + e;
 }

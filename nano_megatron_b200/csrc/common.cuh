@@ -390,11 +390,51 @@ __device__ __forceinline__ uint32_t swz128_offset(uint32_t row, uint32_t chunk16
   return row * 128u + ((chunk16 ^ (row & 7u)) << 4);
 }
 
+// Programmatic dependent launch.  A kernel launched through launch_pdl() may be
+// scheduled while the kernel before it in the stream is still running; it must not
+// touch global memory before pdl_wait(), which returns once every prerequisite grid
+// has completed and its writes are visible.  pdl_launch_dependents() (called right
+// after the wait, so at most one kernel is ever ahead) lets the NEXT kernel's blocks
+// be scheduled as soon as all blocks of this grid have started: launch latency and,
+// where an SM has room, the next kernel's set-up overlap this kernel's execution.
+// Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_enter() {
+  pdl_wait();
+  pdl_launch_dependents();
+}
+
 }  // namespace nmb
 
 // ---------------------------------------------------------------- host side --
 #include <stdio.h>
 namespace nmb {
+
+// One switch for the whole library (nmb_set_pdl): 0 launches every kernel with
+// plain stream ordering.
+inline int g_pdl_enabled = 1;
+
+// Launch `kern` with the programmatic-stream-serialization attribute (see
+// pdl_wait above); the kernel must call pdl_enter() / pdl_wait() before its
+// first global access.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,

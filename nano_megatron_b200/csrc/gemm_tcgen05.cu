@@ -830,6 +830,10 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tma_a, const C
     m_blk = ((rem / tpc) * fc.seq_len + owner * fc.shard_len) / kBM + rem % tpc;
   };
 
+  // The fused forms read and publish protocol words in global memory during set-up:
+  // they order themselves after the previous kernel first.  The plain form sets up
+  // barriers and TMEM first and waits just before its first load.
+  if constexpr (FUSED) pdl_enter();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -862,6 +866,7 @@ __device__ __forceinline__ void gemm_bf16_body(const CUtensorMap& tma_a, const C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if constexpr (!FUSED) pdl_enter();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer --
@@ -1255,6 +1260,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   cluster_sync_all();  // both CTAs' barriers exist before anyone signals across
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_enter();  // set-up above touches no global memory
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer --
@@ -1421,13 +1427,15 @@ static int launch_gemm_pair(const void* A, int lda, const void* B, int ldb, cons
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = L::kTotal + 1024 + kEpiStageBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see pdl_wait()
+  attr[1].val.programmaticStreamSerializationAllowed = g_pdl_enabled;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   int& resident = g_pair_clusters[A_MN][B_MN];
   if (resident == 0) {
     cfg.gridDim = dim3(2 * (sm_count() / 2));
@@ -1489,8 +1497,14 @@ static int launch_gemm_impl(const void* A, int lda, const void* B, int ldb, cons
     const int compute = sm_count() - fc.ag_copy_ctas;
     grid = (tiles < compute ? tiles : compute) + fc.ag_copy_ctas;
   }
-  kern<<<grid, kGemmThreads, smem_bytes, stream>>>(ta, tb, ep, fc, M, N, K, status);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (fc.rs_mode == 0 && fc.ag_copy_ctas == 0) {
+    e = launch_pdl(kern, dim3(grid), dim3(kGemmThreads), smem_bytes, stream, ta, tb, ep, fc, M, N, K, status);
+  } else {
+    // kernels that wait for other GPUs keep plain stream ordering
+    kern<<<grid, kGemmThreads, smem_bytes, stream>>>(ta, tb, ep, fc, M, N, K, status);
+    e = cudaGetLastError();
+  }
   return e == cudaSuccess ? 0 : 400 + static_cast<int>(e);
 }
 

@@ -208,3 +208,9 @@ extern "C" int nmb_scalar_ratio(float* y, const float* num, const float* den, fl
   scale_by_device_scalar_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(y, num, den, mul);
   NMB_LAUNCH_CHECK();
 }
+
+// 1: the GEMM, attention, norm and column-sum kernels are launched with
+// programmatic stream serialization (see pdl_wait in common.cuh); 0: plain
+// stream order for every kernel.
+extern "C" void nmb_set_pdl(int enabled) { nmb::g_pdl_enabled = enabled ? 1 : 0; }
+

@@ -78,6 +78,7 @@ __global__ void norm_fwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const _
                                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, float eps,
                                     int rms) {
   constexpr int H = 256 * V;
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
@@ -144,6 +145,7 @@ __global__ void norm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const 
                                     __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int rms) {
   constexpr int H = 256 * V;
   extern __shared__ float red[];  // [warps][2][H]
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int warps_per_block = blockDim.x >> 5;
@@ -246,6 +248,7 @@ __global__ void norm_bwd_finish_kernel(const float* __restrict__ partial, int n_
                                        __nv_bfloat16* __restrict__ dgamma, __nv_bfloat16* __restrict__ dbeta,
                                        int accumulate) {
   __shared__ float red[8][32];
+  pdl_enter();
   const int cx = threadIdx.x & 31;
   const int px = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + cx;  // column in [0, 2H): dgamma then dbeta
@@ -423,6 +426,7 @@ col_reduce_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16*
   constexpr int mode = MODE;
   __shared__ __align__(16) float red[2][8][256];
   __shared__ int is_last;
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int S = gridDim.y;
@@ -580,9 +584,9 @@ using namespace nmb;
 template <int V>
 static void launch_fwd_vec(const void* x, const void* w, const void* bias, void* y, float* mean, float* rstd, int rows,
                            float eps, int rms, int blocks, cudaStream_t s) {
-  norm_fwd_vec_kernel<V><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-                                               static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(y),
-                                               mean, rstd, rows, eps, rms);
+  launch_pdl(norm_fwd_vec_kernel<V>, dim3(blocks), dim3(256), 0, s, static_cast<const __nv_bfloat16*>(x),
+             static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(bias),
+             static_cast<__nv_bfloat16*>(y), mean, rstd, rows, eps, rms);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -647,9 +651,10 @@ extern "C" int nmb_norm_configure() {
 template <int V>
 static void launch_bwd_vec(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                            const void* dx_add, void* dx, float* partial, int rows, int rms, int blocks, cudaStream_t s) {
-  norm_bwd_vec_kernel<V><<<blocks, 256, 8 * 2 * 256 * V * sizeof(float), s>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
-      mean, rstd, static_cast<const __nv_bfloat16*>(dx_add), static_cast<__nv_bfloat16*>(dx), partial, rows, rms);
+  launch_pdl(norm_bwd_vec_kernel<V>, dim3(blocks), dim3(256), 8 * 2 * 256 * V * sizeof(float), s,
+             static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+             static_cast<const __nv_bfloat16*>(w), mean, rstd, static_cast<const __nv_bfloat16*>(dx_add),
+             static_cast<__nv_bfloat16*>(dx), partial, rows, rms);
 }
 
 // Fused backward: dx, dgamma, dbeta in one pass over dy and x.  Needs
@@ -678,8 +683,8 @@ extern "C" int nmb_norm_bwd_fused(const void* dy, const void* x, const void* w, 
     case 4: launch_bwd_vec<4>(dy, x, w, mean, rstd, dx_add, dx, partial, rows, rms, blocks, s); break;
     default: return -1;
   }
-  norm_bwd_finish_kernel<<<2 * H / 32, 256, 0, s>>>(partial, blocks, H, static_cast<__nv_bfloat16*>(dgamma),
-                                                    static_cast<__nv_bfloat16*>(dbeta), accumulate);
+  launch_pdl(norm_bwd_finish_kernel, dim3(2 * H / 32), dim3(256), 0, s, static_cast<const float*>(partial), blocks, H,
+             static_cast<__nv_bfloat16*>(dgamma), static_cast<__nv_bfloat16*>(dbeta), accumulate);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + e;
 }
@@ -699,13 +704,13 @@ extern "C" int nmb_col_reduce(const void* dy, int ld, const void* x, const float
     while (split < kColSplit && groups * split < 2 * sm_count()) split *= 2;
     while (split > 1 && split * 8 > rows) split /= 2;
     if (mode == 1)
-      col_reduce_vec_kernel<1><<<dim3(groups, split), 256, 0, s>>>(
-          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows, H,
-          ld, rms, static_cast<__nv_bfloat16*>(out0), static_cast<__nv_bfloat16*>(out1), accumulate);
+      launch_pdl(col_reduce_vec_kernel<1>, dim3(groups, split), dim3(256), 0, s,
+                 static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows,
+                 H, ld, rms, static_cast<__nv_bfloat16*>(out0), static_cast<__nv_bfloat16*>(out1), accumulate);
     else
-      col_reduce_vec_kernel<0><<<dim3(groups, split), 256, 0, s>>>(
-          static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows, H,
-          ld, rms, static_cast<__nv_bfloat16*>(out0), static_cast<__nv_bfloat16*>(out1), accumulate);
+      launch_pdl(col_reduce_vec_kernel<0>, dim3(groups, split), dim3(256), 0, s,
+                 static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x), mean, rstd, partial, rows,
+                 H, ld, rms, static_cast<__nv_bfloat16*>(out0), static_cast<__nv_bfloat16*>(out1), accumulate);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : 400 + e;
   }

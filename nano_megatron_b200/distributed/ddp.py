@@ -44,7 +44,7 @@ if TYPE_CHECKING:
 class DistributedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, ctx: "ParallelContext", *, bucket_cap_mb: float = 25.0,
                  broadcast_buffers: bool = False, persistent_grads: Optional[bool] = None,
-                 overlap: Optional[bool] = None) -> None:
+                 overlap: Optional[bool] = None, overwrite_first_grad: bool = False) -> None:
         super().__init__()
         _ = broadcast_buffers  # reserved, as in the reference
         self.add_module("module", module)
@@ -80,6 +80,10 @@ class DistributedDataParallel(nn.Module):
         self._side_stream = torch.cuda.Stream(device=device) if self._overlap else None
         self._side_used = False
         self._flat_buffers: list[torch.Tensor] = []
+        # "first write of a step overwrites" (see zero_grad): off | learning | on
+        self._overwrite_first = bool(overwrite_first_grad)
+        self._grad_trace: Optional[dict[int, str]] = None
+        self._zero_plan: Optional[tuple[list[tuple[int, int, int]], list[nn.Parameter]]] = None
         #: buckets in the order their reduction was issued on the side stream this step, and an event after each
         self._issued: list[GradBucket] = []
         self._bucket_events: dict[int, torch.cuda.Event] = {}
@@ -267,8 +271,56 @@ class DistributedDataParallel(nn.Module):
         if not self._persistent:
             super().zero_grad(set_to_none=set_to_none)
             return
-        for flat in self._flat_buffers:
-            flat.zero_()
+        if self._overwrite_first and self._zero_plan is None:
+            self._learn_zero_plan()
+        if self._zero_plan is not None:
+            ranges, covered = self._zero_plan
+            for i, lo, hi in ranges:
+                self._flat_buffers[i][lo:hi].zero_()
+            for p in covered:
+                p._nmb_overwrite_next = True
+        else:
+            for flat in self._flat_buffers:
+                flat.zero_()
         for b in self._buckets:
             for p, view in zip(b.params, b._views):
                 p.grad = view
+
+    def _learn_zero_plan(self) -> None:
+        """With ``overwrite_first_grad`` the memset of the gradient buffers is replaced,
+        for every parameter whose first gradient write of a step comes from a kernel
+        that can store instead of add (weight-gradient GEMMs, bias column sums, norm
+        backward), by a flag that makes that first write overwrite.  Which parameters
+        qualify is learnt from one traced backward pass between two ``zero_grad``
+        calls; the rest (scatter-added embeddings, gradients that arrive through
+        autograd) keep being zeroed, as merged ranges of the flat buffers.  Only for
+        callers that run exactly one backward pass per ``zero_grad`` with a static
+        model (``Trainer``): a parameter that qualified and then receives no gradient
+        in some step would keep its previous gradient."""
+        from ..ops import functional as F
+
+        if self._grad_trace is None:                      # first call: trace the coming backward pass
+            self._grad_trace = {}
+            F._GRAD_TRACES.append(self._grad_trace)
+            return
+        if not self._grad_trace:                          # no backward pass ran in between: keep tracing
+            return
+        trace, self._grad_trace = self._grad_trace, None
+        F._GRAD_TRACES[:] = [t for t in F._GRAD_TRACES if t is not trace]
+        ranges: list[tuple[int, int, int]] = []
+        covered: list[nn.Parameter] = []
+        for i, b in enumerate(self._buckets):
+            offset = 0
+            for p in b.params:
+                n = p.numel()
+                if trace.get(id(p)) == "direct" and not getattr(p, "_nmb_sp_replicated", False):
+                    covered.append(p)
+                elif ranges and ranges[-1][0] == i and ranges[-1][2] == offset:
+                    ranges[-1] = (i, ranges[-1][1], offset + n)
+                else:
+                    ranges.append((i, offset, offset + n))
+                offset += n
+        if not covered or len(ranges) > len(self._flat_buffers):
+            self._overwrite_first = False                 # would cost more launches than it saves
+            return
+        self._zero_plan = (ranges, covered)

@@ -267,6 +267,8 @@ class _SPEmbeddingFn(torch.autograd.Function):
                                   dy.contiguous(), None, d_pos, vocab_start)
         for param, direct in ((tok_w, tok_direct), (pos_w, pos_direct)):
             if param is not None and direct:
+                from ..ops.functional import note_grad_write
+                note_grad_write(param, False)   # scatter-add into the gradient buffer
                 ready = getattr(param, "_nmb_grad_ready", None)
                 if ready is not None:
                     ready()

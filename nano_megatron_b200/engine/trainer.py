@@ -37,7 +37,9 @@ class Trainer:
         self.model = model
         self.ctx = ctx
         self.graph_error: Optional[str] = None
-        self.ddp = DistributedDataParallel(model, ctx, bucket_cap_mb=bucket_cap_mb)
+        # one backward pass per zero_grad and a static model: the first gradient write of a
+        # step may overwrite instead of a memset + add (see DistributedDataParallel.zero_grad)
+        self.ddp = DistributedDataParallel(model, ctx, bucket_cap_mb=bucket_cap_mb, overwrite_first_grad=True)
         self.optimizer = AdamW(model.named_parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         self._loss_fn = loss_fn or model.shifted_cross_entropy
         #: reductions the optimizer update overlaps with (see ``_step_body``)

@@ -34,14 +34,41 @@ def use_native(t: Tensor) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16
 
 
+# First write of a step overwrites.  A gradient buffer need not be zeroed when the
+# first kernel that writes it in a step stores instead of adding: the owner of the
+# buffers (the data-parallel wrapper) sets ``param._nmb_overwrite_next`` in place
+# of the memset, and the first delivery below clears it.  To learn which parameters
+# qualify it traces one backward pass: every writer of a ``main_grad`` reports
+# here, "direct" when it can overwrite, "other" when it can only add (scatter-add,
+# autograd accumulation); only parameters whose FIRST write was "direct" qualify.
+_GRAD_TRACES: list[dict[int, str]] = []
+
+
+def note_grad_write(param: Optional[Tensor], direct: bool) -> None:
+    if param is None:
+        return
+    for trace in _GRAD_TRACES:
+        trace.setdefault(id(param), "direct" if direct else "other")
+
+
+def take_overwrite(param: Optional[Tensor]) -> bool:
+    """True (once) when the next write to ``param.main_grad`` must overwrite it."""
+    if param is not None and getattr(param, "_nmb_overwrite_next", False):
+        param._nmb_overwrite_next = False
+        return True
+    return False
+
+
 def _deliver_grad(param: Optional[Tensor], compute, *, shape_like: Optional[Tensor] = None):
     """Run ``compute(out, accumulate)``; returns the grad for autograd or None
-    when it was accumulated into ``param.main_grad``."""
+    when it was written into ``param.main_grad`` (added, or stored when the
+    buffer's owner asked for the first write of the step to overwrite)."""
     main = getattr(param, "main_grad", None) if param is not None else None
     if main is not None and getattr(param, "_nmb_sp_replicated", False):
         main = None  # its TP gradient hook only runs on the autograd path
     if main is not None:
-        compute(main, True)
+        note_grad_write(param, True)
+        compute(main, not take_overwrite(param))
         ready = getattr(param, "_nmb_grad_ready", None)
         if ready is not None:
             ready()
@@ -281,8 +308,16 @@ class _NormFn(torch.autograd.Function):
         targets = _norm_grad_targets(w_param, b_param, want_bias)
         if targets is not None:
             bufs, params = targets
+            for p in params:
+                note_grad_write(p, True)
+            flagged = [take_overwrite(p) for p in params]
+            overwrite = all(flagged)
+            if any(flagged) and not overwrite:   # never in practice: both belong to one module
+                for p, f in zip(params, flagged):
+                    if f:
+                        p.main_grad.zero_()
             dx, _, _ = kernels.norm_bwd(dy, x, weight, mean, rstd, ctx.rms, dx_add=dres, want_bias=want_bias,
-                                        grad_out=bufs)
+                                        grad_out=bufs, accumulate=not overwrite)
             for p in params:
                 ready = getattr(p, "_nmb_grad_ready", None)
                 if ready is not None:
@@ -409,6 +444,7 @@ class _EmbeddingFn(torch.autograd.Function):
         run(d_tok, d_pos)
         for param, main in ((tok_w, tok_main), (pos_w, pos_main)):
             if param is not None and main is not None:
+                note_grad_write(param, False)   # a scatter-add: needs what is already there
                 ready = getattr(param, "_nmb_grad_ready", None)
                 if ready is not None:
                     ready()

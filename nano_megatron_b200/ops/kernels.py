@@ -50,11 +50,12 @@ _norm_partial: dict[tuple[int, int], torch.Tensor] = {}
 
 
 def norm_bwd(dy, x, w, mean, rstd, rms: bool, dx_add: Optional[torch.Tensor] = None, want_bias: bool = True,
-             grad_out: Optional[tuple] = None):
+             grad_out: Optional[tuple] = None, accumulate: bool = True):
     """``(dx, dgamma, dbeta)``.  ``dx_add`` is added to dx (the gradient of a
     residual branch that bypassed the norm).  ``grad_out = (dgamma_buf,
-    dbeta_buf)`` makes the kernels ADD the parameter gradients to those bf16
-    buffers; the returned dgamma / dbeta are then None."""
+    dbeta_buf)`` makes the kernels write the parameter gradients to those bf16
+    buffers (added to their contents, or stored with ``accumulate=False``); the
+    returned dgamma / dbeta are then None."""
     dy, x = _bf16(dy), _bf16(x)
     h = x.shape[-1]
     rows = x.numel() // h
@@ -63,6 +64,7 @@ def norm_bwd(dy, x, w, mean, rstd, rms: bool, dx_add: Optional[torch.Tensor] = N
     if dx_add is not None:
         dx_add = _bf16(dx_add)
     acc = grad_out is not None
+    add = acc and accumulate
     if h % 256 == 0 and h <= 1024:
         # one pass over dy and x: dx plus the column sums for dgamma / dbeta
         key = (x.device.index or 0, h)
@@ -78,7 +80,7 @@ def norm_bwd(dy, x, w, mean, rstd, rms: bool, dx_add: Optional[torch.Tensor] = N
         rc = lib.nmb_norm_bwd_fused(native.ptr(dy), native.ptr(x), native.ptr(_bf16(w)), native.ptr(mean),
                                     native.ptr(rstd), native.ptr(dx_add), native.ptr(dx), native.ptr(dw),
                                     native.ptr(db), native.ptr(partial), c_int(rows), c_int(h), c_int(int(rms)),
-                                    c_int(int(acc)), native.stream_ptr(x.device))
+                                    c_int(int(add)), native.stream_ptr(x.device))
         if rc == 0:
             native.launches += 2
             return (dx, None, None) if acc else (dx, dw, db)
@@ -95,7 +97,7 @@ def norm_bwd(dy, x, w, mean, rstd, rms: bool, dx_add: Optional[torch.Tensor] = N
         db = torch.empty(h, dtype=torch.bfloat16, device=x.device) if want_bias else None
     rc = lib.nmb_col_reduce(native.ptr(dy), c_int(h), native.ptr(x), native.ptr(mean), native.ptr(rstd),
                             native.ptr(_col_scratch(x.device, h)), native.ptr(dw), native.ptr(db), c_int(rows),
-                            c_int(h), c_int(1), c_int(int(rms)), c_int(int(acc)), native.stream_ptr(x.device))
+                            c_int(h), c_int(1), c_int(int(rms)), c_int(int(add)), native.stream_ptr(x.device))
     native.check_rc(rc, "nmb_col_reduce")
     return (dx, None, None) if acc else (dx, dw, db)
 

@@ -101,6 +101,9 @@ def lib() -> ctypes.CDLL:
                 pair = os.environ.get("NMB_GEMM_PAIR")
                 if pair is not None:
                     _lib.nmb_gemm_set_pair(int(pair != "0"))
+                pdl = os.environ.get("NMB_PDL")      # "0": plain stream order for every kernel
+                if pdl is not None:
+                    _lib.nmb_set_pdl(int(pdl != "0"))
     _configure_current_device(_lib)
     return _lib
 

@@ -162,3 +162,79 @@ def test_1f1b_with_data_parallel_replicas_syncs_once_at_the_end():
         mean = [(a + b) / 2 for a, b in zip(want[0][stage_index], want[1][stage_index])]
         assert all(torch.allclose(g, w, atol=1e-5) for g, w in zip(grads, mean))
         assert n_sync == 1                                       # one bucket, reduced once after the last microbatch
+
+
+# ------------------------------------------------- first write overwrites --
+class _DirectLinear(torch.autograd.Function):
+    """y = x W^T whose weight gradient goes straight into ``weight.main_grad``
+    through the framework's delivery helper (what the GEMM backward does on a GPU)."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x)
+        ctx.weight = weight
+        return x @ weight.t()
+
+    @staticmethod
+    def backward(ctx, dy):
+        from nano_megatron_b200.ops.functional import _deliver_grad
+
+        (x,) = ctx.saved_tensors
+
+        def compute(out, accumulate):
+            g = dy.t() @ x
+            if out is None:
+                return g
+            if accumulate:
+                out.add_(g)
+            else:
+                out.copy_(g)
+            return None
+
+        return dy @ ctx.weight, _deliver_grad(ctx.weight, compute)
+
+
+class _Toy(nn.Module):
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(5)
+        self.emb = nn.Embedding(11, 6)          # gradient arrives through autograd: must keep being zeroed
+        self.w1 = nn.Parameter(torch.randn(8, 6) * 0.3)
+        self.w2 = nn.Parameter(torch.randn(3, 8) * 0.3)
+
+    def forward(self, ids):
+        return _DirectLinear.apply(torch.tanh(_DirectLinear.apply(self.emb(ids), self.w1)), self.w2)
+
+
+def test_first_gradient_write_of_a_step_overwrites_instead_of_a_memset():
+    """After one traced backward pass the wrapper zeroes only the parameters whose
+    gradient cannot be stored by its first writer; the others get a flag that makes
+    that writer overwrite.  Gradients match plain autograd on every step, stale
+    values included (the buffers are poisoned before each zero_grad)."""
+
+    def rank_fn(rank, be):
+        ctx = thread_context(rank, be, dp=1)
+        toy = _Toy()
+        ddp = DistributedDataParallel(toy, ctx, persistent_grads=True, overwrite_first_grad=True)
+        plain = _Toy()
+        out = []
+        for step in range(4):
+            ids = torch.randint(0, 11, (5,), generator=torch.Generator().manual_seed(step))
+            for flat in ddp._flat_buffers:
+                flat.fill_(123.0)                                  # whatever the last step left
+            ddp.zero_grad()
+            ddp(ids).square().sum().backward()
+            ddp.finish_grad_sync()
+            plain.zero_grad()
+            plain(ids).square().sum().backward()
+            out.append([(n, p.grad.clone(), q.grad.clone()) for (n, p), q in
+                        zip(toy.named_parameters(), plain.parameters())])
+        return out, ddp._zero_plan
+
+    (steps, plan), = run_ranks(1, rank_fn)
+    for grads in steps:
+        for name, got, want in grads:
+            assert torch.allclose(got, want, atol=1e-6), name
+    ranges, covered = plan
+    assert {tuple(p.shape) for p in covered} == {(8, 6), (3, 8)}      # the two direct weights
+    assert len(ranges) == 1 and ranges[0][2] - ranges[0][1] == 11 * 6  # only the embedding is still zeroed
