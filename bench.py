@@ -76,6 +76,7 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--no-symm", action="store_true", help="plain NCCL collectives instead of peer-memory kernels")
     ap.add_argument("--mode-steps", type=int, default=30, help="timed steps of each entry under 'modes'")
     ap.add_argument("--no-modes", action="store_true", help="headline only")
+    ap.add_argument("--bucket-mb", type=float, default=25.0, help="gradient bucket size of the data-parallel wrapper")
     args = ap.parse_args()
     args.explicit_mode = args.mode is not None
     if args.mode is None:
@@ -480,7 +481,7 @@ class B200Runner:
                                            weight_decay=0.01, use_cuda_graph=not self.args.no_graph)
         else:
             model = build_tp_gpt_from_reference(ref, self.ctx).to(dev, dtype=torch.bfloat16)
-            self.trainer = Trainer(model, self.ctx, lr=1e-4, weight_decay=0.01,
+            self.trainer = Trainer(model, self.ctx, lr=1e-4, weight_decay=0.01, bucket_cap_mb=self.args.bucket_mb,
                                    use_cuda_graph=not self.args.no_graph)
         del ref
 

@@ -77,9 +77,18 @@ class DistributedDataParallel(nn.Module):
         self._on_gpu = device.type == "cuda"
         self._persistent = self._on_gpu if persistent_grads is None else bool(persistent_grads)
         self._overlap = self._on_gpu if overlap is None else bool(overlap and self._on_gpu)
-        self._side_stream = torch.cuda.Stream(device=device) if self._overlap else None
+        # High priority: a bucket reduction is a few dozen blocks that must become resident
+        # beside whatever the compute stream is running.  At default priority the reduction of
+        # the last bucket waited behind the 16 k blocks of the optimizer kernel it was meant to
+        # overlap (373 us exposed per step at two ranks); kernel nodes keep the priority under
+        # CUDA-graph capture.
+        self._side_stream = torch.cuda.Stream(device=device, priority=-1) if self._overlap else None
         self._side_used = False
         self._flat_buffers: list[torch.Tensor] = []
+        #: Called with a bucket right after its reduction has been issued, on the stream the
+        #: reduction runs on (so work launched from the callback is ordered after it).  The
+        #: trainer uses it to update a bucket's parameters while backward is still running.
+        self.after_bucket_sync: Optional[Any] = None
         # "first write of a step overwrites" (see zero_grad): off | learning | on
         self._overwrite_first = bool(overwrite_first_grad)
         self._grad_trace: Optional[dict[int, str]] = None
@@ -193,6 +202,8 @@ class DistributedDataParallel(nn.Module):
             self._side_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self._side_stream):
                 bucket.sync(self._backend, self._dp_group, self._mean_divisor, group_size=self._sync_group_size)
+                if self.after_bucket_sync is not None:
+                    self.after_bucket_sync(bucket)
                 event = self._bucket_events.get(id(bucket))
                 if event is None:
                     event = self._bucket_events[id(bucket)] = torch.cuda.Event()
@@ -201,6 +212,8 @@ class DistributedDataParallel(nn.Module):
             self._side_used = True
         else:
             bucket.sync(self._backend, self._dp_group, self._mean_divisor, group_size=self._sync_group_size)
+            if self.after_bucket_sync is not None:
+                self.after_bucket_sync(bucket)
 
     # --------------------------------------------------------------- forward --
     def forward(self, *args: Any, **kwargs: Any) -> Any:

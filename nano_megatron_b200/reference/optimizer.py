@@ -101,11 +101,11 @@ class AdamW:
         key = tuple((n, p.data_ptr(), p.grad.data_ptr()) for n, p in live)
         plan = self._plans.get(key)
         if plan is None:
-            # a plan per distinct parameter subset (the whole model, or the two halves of a split update)
+            # a plan per distinct parameter subset (the whole model, one gradient bucket, ...)
             states = [self._ensure_state(n, p) for n, p in live]
             plan = FusedAdamWPlan(key, [p for _, p in live], states)
             plan.names = [n for n, _ in live]
-            if len(self._plans) >= 4:
+            if len(self._plans) >= 512:          # one per gradient bucket at most, in practice
                 self._plans.clear()
             self._plans[key] = plan
         self._fused = plan
