@@ -109,6 +109,42 @@ def worker_groups():
     assert not P.is_parallel_initialized() and not dist.is_initialized()
 
 
+def worker_symmetric_backend_falls_back():
+    """``SymmetricBackend`` without a GPU (no workspace, CPU tensors): every method of
+    the protocol gives the library's result and is counted as a library call."""
+    from nano_megatron_b200.distributed import SymmetricBackend
+    import nano_megatron_b200.parallel as P
+    be = SymmetricBackend()
+    ctx = P.initialize_parallel(P.ParallelConfig(), dist_backend="gloo", backend=be)
+    assert ctx.backend is be
+    n, r = ctx.world_size, ctx.rank
+    x = torch.full((5,), float(r + 1))
+    assert be.all_reduce(x).tolist() == [float(n * (n + 1) // 2)] * 5
+    assert be.all_reduce(torch.full((2,), float(r)), op="max", async_op=True).wait() is not None
+    out = torch.empty(n * 3)
+    be.all_gather_into_tensor(out, torch.full((3,), float(r)))
+    assert out.view(n, 3)[:, 0].tolist() == [float(i) for i in range(n)]
+    lst = [torch.empty(2) for _ in range(n)]
+    be.all_gather(lst, torch.full((2,), float(r)))
+    assert [t[0].item() for t in lst] == [float(i) for i in range(n)]
+    rs = torch.empty(4)
+    be.reduce_scatter(rs, [torch.full((4,), float(i + r)) for i in range(n)])
+    assert rs[0].item() == float(sum(r + i for i in range(n)))
+    b = torch.full((3,), float(r))
+    be.broadcast(b, n - 1)
+    assert b[0].item() == n - 1
+    be.barrier()
+    if r == 0:
+        be.send(torch.tensor([7.0]), 1)
+    elif r == 1:
+        assert be.recv(torch.empty(1), 0).item() == 7.0
+    assert be.counts and all(k.endswith(":library") for k in be.counts), be.counts
+    assert {k.split(":")[0] for k in be.counts} == {"all_reduce", "all_gather_into_tensor", "all_gather",
+                                                    "reduce_scatter", "broadcast", "barrier"}
+    dist.barrier()
+    P.destroy_parallel()
+
+
 def _tp_worker(sp: bool, **knobs):
     from nano_megatron_b200.models import build_tp_gpt_from_reference
     P, ctx = _setup(tensor_parallel_size=2, sequence_parallel=sp)
@@ -363,7 +399,7 @@ def worker_cp2_dp2():
 
 # ---------------------------------------------------------------- launchers --
 CASES = [
-    ("worker_groups", 4), ("worker_tp2", 2), ("worker_tp2_fused_gated_gqa", 2), ("worker_tp2_gpt2_tied", 2),
+    ("worker_groups", 4), ("worker_symmetric_backend_falls_back", 2), ("worker_tp2", 2), ("worker_tp2_fused_gated_gqa", 2), ("worker_tp2_gpt2_tied", 2),
     ("worker_sp2", 2), ("worker_sp2_gpt2", 2), ("worker_sp_equals_tp_on_same_groups", 2),
     ("worker_ddp_mlp", 2), ("worker_ddp_mlp", 4), ("worker_ddp_persistent_mlp", 2), ("worker_tp2_dp2", 4),
     ("worker_pp2", 2), ("worker_pp4_m8", 4), ("worker_tp2_pp2", 4), ("worker_tp2_pp2_sp", 4),

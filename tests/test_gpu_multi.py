@@ -115,6 +115,67 @@ def worker_symm_allreduce():
     _finish(P)
 
 
+def worker_symmetric_backend():
+    """The eight-method ``CommBackend`` on peer-memory kernels: every collective against
+    the NCCL result, the calls counted as "symmetric", and an all-reduce + all-gather
+    captured in a CUDA graph and replayed."""
+    from nano_megatron_b200.distributed import SymmetricBackend, TorchDistBackend
+    from nano_megatron_b200.distributed import symmetric
+    from nano_megatron_b200.distributed.symm_mem import SymmetricWorkspace
+    P, ctx, _ = _setup(symm=False)
+    group = dist.group.WORLD
+    ws = SymmetricWorkspace(group)
+    symmetric.register_workspace(group, ws)
+    be, lib = SymmetricBackend(), TorchDistBackend()
+    n, r = ws.size, ctx.rank
+    for dtype in (torch.bfloat16, torch.float32):
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+        x = (torch.randn(3, 1001, device="cuda") * (r + 1)).to(dtype)
+        want = lib.all_reduce(x.clone(), group=group)
+        got = be.all_reduce(x.clone(), group=group)
+        assert (got.float() - want.float()).abs().max().item() <= tol * want.float().abs().max().item()
+        out_w, out_g = torch.empty(n * 77, device="cuda", dtype=dtype), torch.empty(n * 77, device="cuda", dtype=dtype)
+        src = torch.full((77,), float(r + 1), device="cuda", dtype=dtype)
+        lib.all_gather_into_tensor(out_w, src, group=group)
+        be.all_gather_into_tensor(out_g, src, group=group)
+        assert torch.equal(out_w, out_g)
+        lst = [torch.empty(5, 9, device="cuda", dtype=dtype) for _ in range(n)]
+        be.all_gather(lst, torch.full((5, 9), float(r), device="cuda", dtype=dtype), group=group)
+        assert all(torch.all(t == i) for i, t in enumerate(lst))
+        parts = [(torch.randn(40, device="cuda") * (r + 1 + i)).to(dtype) for i in range(n)]
+        rs_w, rs_g = torch.empty(40, device="cuda", dtype=dtype), torch.empty(40, device="cuda", dtype=dtype)
+        lib.reduce_scatter(rs_w, [p.clone() for p in parts], group=group)
+        be.reduce_scatter(rs_g, parts, group=group)
+        assert (rs_g.float() - rs_w.float()).abs().max().item() <= tol * max(rs_w.float().abs().max().item(), 1.0)
+        b = torch.full((33,), float(r + 5), device="cuda", dtype=dtype)
+        be.broadcast(b, n - 1, group=group)
+        assert torch.all(b == n - 1 + 5)
+    be.barrier(group=group)
+    assert all(k.endswith(":symmetric") for k in be.counts), be.counts
+    # a reduce op the kernels do not take goes to the library, counted as such
+    m = torch.full((8,), float(r), device="cuda")
+    be.all_reduce(m, group=group, op="max")
+    assert m[0].item() == n - 1 and be.counts.get("all_reduce:library") == 1
+    # the kernel collectives are plain launches: capture two of them and replay
+    x = torch.zeros(1000, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(n * 1000, device="cuda", dtype=torch.bfloat16)
+    be.all_reduce(x, group=group); be.all_gather_into_tensor(out, x, group=group)   # sizes seen before the capture
+    torch.cuda.synchronize(); dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        be.all_reduce(x, group=group)
+        be.all_gather_into_tensor(out, x, group=group)
+    for trial in range(3):
+        x.fill_(float(r + 1 + trial))
+        g.replay()
+        torch.cuda.synchronize()
+        total = float(sum(i + 1 + trial for i in range(n)))
+        assert torch.all(x == total) and torch.all(out == total), (trial, x[0].item(), out[0].item())
+    symmetric.unregister_workspace(group)
+    ws.close()
+    _finish(P)
+
+
 def worker_ddp_symmetric():
     from nano_megatron_b200.distributed import DistributedDataParallel
     P, ctx, made = _setup()
@@ -418,12 +479,13 @@ def worker_trainer_graph_tp():
     _finish(P)
 
 
-CASES = [("worker_symm_allreduce", 2), ("worker_ddp_symmetric", 2), ("worker_fused_gemm_ops", 2),
+CASES = [("worker_symm_allreduce", 2), ("worker_symmetric_backend", 2), ("worker_ddp_symmetric", 2),
+         ("worker_fused_gemm_ops", 2),
          ("worker_tp_bf16", 2), ("worker_sp_bf16", 2), ("worker_dp_bf16", 2), ("worker_cp_bf16", 2),
          ("worker_pp_trainer", 2), ("worker_trainer_graph_tp", 2),
          # the layouts the benchmark runs at 4 and 8 GPUs
          ("worker_fused_gemm_ops", 4), ("worker_tp_bf16", 4), ("worker_sp_bf16", 4), ("worker_cp_bf16", 4),
-         ("worker_pp_trainer", 4),
+         ("worker_pp_trainer", 4), ("worker_symmetric_backend", 4),
          ("worker_fused_gemm_ops", 8), ("worker_tp_bf16", 8), ("worker_sp_bf16", 8), ("worker_cp_bf16", 8),
          ("worker_dp_bf16", 8), ("worker_ddp_symmetric", 8), ("worker_pp_trainer", 8)]
 
