@@ -37,6 +37,8 @@ import sys
 import threading
 import time
 
+T_START = time.time()
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -77,6 +79,9 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--mode-steps", type=int, default=30, help="timed steps of each entry under 'modes'")
     ap.add_argument("--no-modes", action="store_true", help="headline only")
     ap.add_argument("--bucket-mb", type=float, default=25.0, help="gradient bucket size of the data-parallel wrapper")
+    ap.add_argument("--modes-budget-s", type=float, default=240.0,
+                    help="no further entry under 'modes' is started once the run is this old (wall clock of rank 0); "
+                         "the headline is always measured")
     args = ap.parse_args()
     args.explicit_mode = args.mode is not None
     if args.mode is None:
@@ -369,6 +374,13 @@ def main() -> int:
         sub_steps = max(1, min(args.mode_steps, args.steps))
         for name, ns in extra_specs(args):
             sub = spec_of(ns)
+            # Every configuration costs tens of seconds of set-up (groups, workspaces, capture):
+            # stop adding entries when the run is older than the budget.  Rank 0's clock decides.
+            age = torch.tensor([time.time() - T_START], device=torch.device("cuda", local_rank))
+            dist.broadcast(age, src=0)
+            if age.item() > args.modes_budget_s:
+                modes[name] = {"skipped": f"time budget of {args.modes_budget_s:.0f} s for the sub-results was used up"}
+                continue
             try:
                 modes[name] = mode_entry(sub, measure(ns, sub, sub_steps, max(3, min(args.warmup, 5))), sub_steps)
             except Exception as exc:  # one configuration must not cost the whole line

@@ -111,9 +111,15 @@ class SymmetricBackend(TorchDistBackend):
         pad = (-flat.numel()) % per
         if pad:
             flat = torch.nn.functional.pad(flat, (0, pad))
+        capturing = torch.cuda.is_current_stream_capturing()
         cache = ws.__dict__.get("_ag_cache", {})
-        if (flat.numel() * flat.element_size(), flat.dtype) not in cache and torch.cuda.is_current_stream_capturing():
+        if (flat.numel() * flat.element_size(), flat.dtype) not in cache and capturing:
             return None
+        if capturing:
+            # A replayed graph gathers into the SAME buffer every time (the alternation of
+            # the two result buffers happens on the host): make sure every rank has consumed
+            # the previous replay's result before any peer stores into it again.
+            ws.barrier(CHANNEL_AUX)
         return ws.all_gather(flat.contiguous())[:, : tensor.numel()]
 
     def all_gather_into_tensor(self, output: Tensor, input: Tensor, *, group: Optional[Any] = None) -> Tensor:
