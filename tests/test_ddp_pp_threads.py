@@ -238,3 +238,36 @@ def test_first_gradient_write_of_a_step_overwrites_instead_of_a_memset():
     ranges, covered = plan
     assert {tuple(p.shape) for p in covered} == {(8, 6), (3, 8)}      # the two direct weights
     assert len(ranges) == 1 and ranges[0][2] - ranges[0][1] == 11 * 6  # only the embedding is still zeroed
+
+
+def test_after_bucket_sync_fires_once_per_bucket_and_only_when_the_bucket_is_reduced():
+    """The hook a trainer uses to act on a bucket as soon as its gradients are final."""
+    replicas = [_mlp(3) for _ in range(2)]
+    data = [torch.randn(4, 6, generator=torch.Generator().manual_seed(r)) for r in range(2)]
+    dense = _mlp(3)                                               # built here: threads share the global generator
+    sum(dense(x).square().mean() for x in data).backward()
+    want = {tuple(p.shape): p.grad / 2 for p in dense.parameters()}
+
+    def rank_fn(rank, be):
+        ddp = DistributedDataParallel(replicas[rank], thread_context(rank, be, dp=2), bucket_cap_mb=1e-4)
+        seen: list[int] = []
+        reduced_before_hook: list[bool] = []
+
+        def hook(bucket):
+            seen.append(id(bucket))
+            reduced_before_hook.append(all(torch.allclose(p.grad, want[tuple(p.shape)], atol=1e-6)
+                                           for p in bucket.params))
+
+        ddp.after_bucket_sync = hook
+        with ddp.no_sync():
+            ddp(data[rank]).square().mean().backward()
+        assert not seen                                           # nothing is reduced under no_sync
+        ddp.zero_grad()
+        ddp(data[rank]).square().mean().backward()
+        ddp.finish_grad_sync()
+        ddp.finish_grad_sync()
+        return seen, reduced_before_hook, len(ddp._buckets)
+
+    for seen, ok, n_buckets in run_ranks(2, rank_fn):
+        assert len(seen) == n_buckets == len(set(seen)) == 4       # one call per bucket, none twice
+        assert all(ok)                                             # the hook sees reduced (averaged) gradients
