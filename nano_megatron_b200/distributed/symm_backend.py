@@ -1,6 +1,6 @@
 """``CommBackend`` on this package's peer-memory kernels.
 
-The reference's distributed layer is one protocol (nano_megatron/distributed/backend.py:11-66)
+The reference's distributed layer is one protocol (nano_megatron/distributed/backend.py:8-47)
 with one implementation on ``torch.distributed``.  :class:`SymmetricBackend` is a second
 implementation of the same eight methods: for every process group that has a symmetric-memory
 workspace (``enable_symmetric_memory``) the collectives run as plain CUDA kernels over peer
