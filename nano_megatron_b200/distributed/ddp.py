@@ -158,7 +158,7 @@ class DistributedDataParallel(nn.Module):
     def _register_grad_hooks(self) -> None:
         for param in self._param_to_bucket:
             self._hook_handles.append(
-                param.register_post_accumulate_grad_hook(lambda _p, param=param: self._on_param_grad_ready(param)))
+                param.register_post_accumulate_grad_hook(lambda _p, param=param: self._on_autograd_write(param)))
             # Kernels that accumulate into ``main_grad`` announce it here.
             param._nmb_grad_ready = (lambda param=param: self._on_direct_write(param))
 
@@ -172,6 +172,12 @@ class DistributedDataParallel(nn.Module):
             yield
         finally:
             self._require_backward_grad_sync = prev
+
+    def _on_autograd_write(self, param: nn.Parameter) -> None:
+        # autograd added a gradient to ``.grad``: an adding write as far as the zero plan goes
+        if self._grad_trace is not None:
+            self._grad_trace.setdefault(id(param), "other")
+        self._on_param_grad_ready(param)
 
     def _on_direct_write(self, param: nn.Parameter) -> None:
         if not self._require_backward_grad_sync:
