@@ -12,6 +12,15 @@ from __future__ import annotations
 import itertools
 
 
+def prefix_product(values: list[int], init: int = 1) -> list[int]:
+    """``[init, init*v0, init*v0*v1, ...]``: the stride table of a mixed-radix rank layout
+    (same helper as nano_megatron/parallel/rank_generator.py:4-10)."""
+    out = [init]
+    for v in values:
+        out.append(out[-1] * v)
+    return out
+
+
 def _strides(sizes: list[int]) -> list[int]:
     out, acc = [], 1
     for s in sizes:

@@ -457,3 +457,18 @@ def test_torch_backend_wraps_every_protocol_method(world1):
     assert torch.equal(rs, t)
     assert torch.equal(be.broadcast(t.clone(), 0), t)
     be.barrier()
+
+
+def test_reference_import_paths_and_rank_helpers_exist():
+    """``nano_megatron.model`` / ``.model.tp_gpt`` / ``.model.pipeline`` of the reference map to
+    the same modules here, and the stride helper of the rank generator is public as there."""
+    import nano_megatron_b200.model as alias
+    import nano_megatron_b200.model.pipeline as alias_pp
+    import nano_megatron_b200.model.tp_gpt as alias_tp
+    import nano_megatron_b200.models as models
+    from nano_megatron_b200.parallel.rank_generator import prefix_product
+
+    assert alias_tp is models.tp_gpt and alias_pp is models.pipeline
+    assert set(alias.__all__) == set(models.__all__) and alias.TPGPT is models.TPGPT
+    assert prefix_product([2, 3, 4]) == [1, 2, 6, 24]
+    assert prefix_product([], init=5) == [5]
