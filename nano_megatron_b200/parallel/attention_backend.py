@@ -110,17 +110,25 @@ def flash_causal_attention(q: Tensor, k: Tensor, v: Tensor, *, scale: float, dro
 def _online_softmax_combine(out_a: Tensor, lse_a: Tensor, out_b: Tensor, lse_b: Tensor) -> tuple[Tensor, Tensor]:
     """Merge two partial attention results over disjoint key sets.
 
-    ``out_*`` are ``[B, S, h, d]`` normalised partial outputs, ``lse_*`` the
-    ``[B, h, S]`` log-sum-exp of their scores; fp32 arithmetic.
+    ``out_*`` are normalised partial outputs, ``lse_*`` the ``[B, h, S]`` log-sum-exp of
+    their scores; fp32 arithmetic.  The outputs may be ``[B, S, h, d]`` (the layout of this
+    package's kernels) or ``[B, h, S, d]`` (the reference's helper,
+    nano_megatron/parallel/attention_backend.py:227-270); the layout is read off the shapes
+    and ``[B, S, h, d]`` is assumed when ``h == S`` makes them indistinguishable.
     """
+    if out_a.shape != out_b.shape or lse_a.shape != lse_b.shape:
+        raise ValueError(f"partial results must share shapes; got {tuple(out_a.shape)} vs {tuple(out_b.shape)} "
+                         f"and {tuple(lse_a.shape)} vs {tuple(lse_b.shape)}")
     lse_a, lse_b = lse_a.float(), lse_b.float()
     top = torch.maximum(lse_a, lse_b)
     wa, wb = torch.exp(lse_a - top), torch.exp(lse_b - top)
     total = wa + wb
     lse = top + torch.log(total)
-    ca = (wa / total).transpose(1, 2).unsqueeze(-1)
-    cb = (wb / total).transpose(1, 2).unsqueeze(-1)
-    return (out_a.float() * ca + out_b.float() * cb).to(out_a.dtype), lse
+    ca, cb = wa / total, wb / total
+    heads_first = tuple(out_a.shape[1:3]) == tuple(lse.shape[1:3]) and out_a.shape[1] != out_a.shape[2]
+    if not heads_first:
+        ca, cb = ca.transpose(1, 2), cb.transpose(1, 2)
+    return (out_a.float() * ca.unsqueeze(-1) + out_b.float() * cb.unsqueeze(-1)).to(out_a.dtype), lse
 
 
 class _FlashChunkedCPCausalAttention(torch.autograd.Function):

@@ -259,7 +259,9 @@ class _ReduceFromTPRegion(torch.autograd.Function):
             buf = buffer_manager.get_buffer(x.shape, x.dtype, x.device)
             buf.copy_(x)
             x = buf
-        else:
+        elif not (x.is_leaf and x.requires_grad):
+            # reduced in place and handed back: tell autograd (a leaf that requires grad
+            # cannot be marked; it is returned as it is, like the reference does)
             ctx.mark_dirty(x)
         _wait(backend.all_reduce(x, group=group, op="sum", async_op=True))
         return x

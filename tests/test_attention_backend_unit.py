@@ -110,3 +110,28 @@ def test_online_softmax_merge_of_two_key_ranges_equals_attention_over_their_unio
     # merging is symmetric
     out2, lse2 = AB._online_softmax_combine(out_b, lse_b, out_a, lse_a)
     assert torch.allclose(out2, out, atol=1e-6) and torch.allclose(lse2, lse, atol=1e-6)
+
+
+@pytest.mark.parametrize("heads_first", [False, True])
+def test_partial_attention_merge_accepts_both_output_layouts(heads_first):
+    """Two partial attentions over disjoint key sets merged by their log-sum-exps equal
+    attention over all keys, for outputs laid out ``[B, S, h, d]`` or ``[B, h, S, d]``."""
+    from nano_megatron_b200.parallel.attention_backend import _online_softmax_combine
+
+    torch.manual_seed(0)
+    b, h, s, d = 2, 3, 5, 4
+    q = torch.randn(b, h, s, d)
+    parts, scores = [], []
+    for n_keys in (6, 7):
+        k, v = torch.randn(b, h, n_keys, d), torch.randn(b, h, n_keys, d)
+        sc = q @ k.transpose(-2, -1) * d ** -0.5
+        scores.append(sc)
+        parts.append((torch.softmax(sc, -1) @ v, torch.logsumexp(sc, -1), v))
+    full = torch.cat(scores, -1)
+    want = torch.softmax(full, -1) @ torch.cat([p[2] for p in parts], 2)
+    lay = (lambda t: t) if heads_first else (lambda t: t.transpose(1, 2).contiguous())
+    out, lse = _online_softmax_combine(lay(parts[0][0]), parts[0][1], lay(parts[1][0]), parts[1][1])
+    torch.testing.assert_close(out, lay(want), atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(lse, torch.logsumexp(full, -1), atol=1e-5, rtol=1e-5)
+    with pytest.raises(ValueError):
+        _online_softmax_combine(parts[0][0], parts[0][1], parts[1][0][:, :, :2], parts[1][1])

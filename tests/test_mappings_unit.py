@@ -175,3 +175,22 @@ def test_rank_generator_groups_partition_the_world_and_round_trip(order):
         assert gen.encode(gen.decode(rank)) == rank
     fastest = order.split("-")[0]
     assert gen.get_ranks(fastest)[0] == [0, 1]                # the first dimension of the order is contiguous
+
+
+def test_reduce_from_tp_region_takes_a_leaf_that_requires_grad():
+    """The in-place reduction may be applied to a leaf tensor that requires grad (the
+    reference's function allows it); backward is the identity."""
+    from nano_megatron_b200.parallel.mappings import _ReduceFromTPRegion
+
+    class _Sum1:
+        def all_reduce(self, tensor, *, group=None, op="sum", async_op=False):
+            return None
+
+    x = torch.randn(3, 4, requires_grad=True)
+    y = _ReduceFromTPRegion.apply(x, None, _Sum1())
+    y.sum().backward()
+    assert torch.equal(x.grad, torch.ones_like(x))
+    a = torch.randn(3, 4, requires_grad=True)
+    z = _ReduceFromTPRegion.apply(a * 2.0, None, _Sum1())          # the usual case: an activation
+    z.sum().backward()
+    assert torch.equal(a.grad, torch.full_like(a, 2.0))
