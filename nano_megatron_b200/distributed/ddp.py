@@ -28,6 +28,7 @@ B200-first differences:
 """
 from __future__ import annotations
 
+import weakref
 from contextlib import contextmanager
 from typing import TYPE_CHECKING, Any, Iterator, Optional
 
@@ -319,8 +320,11 @@ class DistributedDataParallel(nn.Module):
         from ..ops import functional as F
 
         if self._grad_trace is None:                      # first call: trace the coming backward pass
-            self._grad_trace = {}
-            F._GRAD_TRACES.append(self._grad_trace)
+            trace = self._grad_trace = {}
+            F._GRAD_TRACES.append(trace)
+            # a wrapper that is dropped before it finished learning must not stay registered
+            weakref.finalize(self, lambda t=trace: F._GRAD_TRACES.__setitem__(
+                slice(None), [x for x in F._GRAD_TRACES if x is not t]))
             return
         if not self._grad_trace:                          # no backward pass ran in between: keep tracing
             return
