@@ -542,6 +542,8 @@ class B200Runner:
             self.note = f"not every step kind runs from a CUDA graph: {self.trainer.graph_error}"
 
     def close(self) -> None:
+        if self.trainer is not None:
+            self.trainer.close()        # graphs and gradient hooks would keep the model alive
         self.trainer = None
         self.P.destroy_parallel()
 

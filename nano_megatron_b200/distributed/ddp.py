@@ -163,6 +163,24 @@ class DistributedDataParallel(nn.Module):
             # Kernels that accumulate into ``main_grad`` announce it here.
             param._nmb_grad_ready = (lambda param=param: self._on_direct_write(param))
 
+    def close(self) -> None:
+        """Detach from the wrapped module: remove the gradient hooks and the per-parameter
+        callbacks.  The hooks are held by the parameters' autograd metadata and refer back to
+        this wrapper, a cycle the garbage collector cannot see through, so a wrapper that is
+        merely dropped keeps its module, gradient buffers and itself alive."""
+        for handle in self._hook_handles:
+            handle.remove()
+        self._hook_handles = []
+        for param in self._param_to_bucket:
+            for attr in ("_nmb_grad_ready", "_nmb_overwrite_next"):
+                if hasattr(param, attr):
+                    delattr(param, attr)
+        self.after_bucket_sync = None
+        if self._grad_trace is not None:
+            from ..ops import functional as F
+            trace, self._grad_trace = self._grad_trace, None
+            F._GRAD_TRACES[:] = [t for t in F._GRAD_TRACES if t is not trace]
+
     # ----------------------------------------------------------------- hooks --
     @contextmanager
     def no_sync(self) -> Iterator[None]:

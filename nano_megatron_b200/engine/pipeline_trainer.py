@@ -123,6 +123,14 @@ class PipelineTrainer:
     def graphed(self) -> bool:
         return bool(self._slots)
 
+    def close(self) -> None:
+        """Drop the captured graphs and detach the data-parallel wrapper from the stage (see
+        ``Trainer.close``)."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self._slots = []
+        self.ddp.close()
+
     def check(self) -> None:
         if self.device.type == "cuda":
             native.check_status(self.device)

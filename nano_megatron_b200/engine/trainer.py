@@ -225,6 +225,17 @@ class Trainer:
     def graphed(self) -> bool:
         return bool(self._graphs)
 
+    def close(self) -> None:
+        """Drop the captured graphs and detach the data-parallel wrapper from the model (its
+        hooks keep model and gradient buffers alive otherwise).  Call it when the trainer is
+        discarded and the process goes on, with no step in flight."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self._graphs.clear()
+        self._tried.clear()
+        self._pool = None
+        self.ddp.close()
+
     def check(self) -> None:
         """Raise if any kernel reported a device-side failure (host sync)."""
         if self.device.type == "cuda":

@@ -271,3 +271,25 @@ def test_after_bucket_sync_fires_once_per_bucket_and_only_when_the_bucket_is_red
     for seen, ok, n_buckets in run_ranks(2, rank_fn):
         assert len(seen) == n_buckets == len(set(seen)) == 4       # one call per bucket, none twice
         assert all(ok)                                             # the hook sees reduced (averaged) gradients
+
+
+def test_close_detaches_the_wrapper_so_that_model_and_buffers_can_be_freed():
+    """The gradient hooks live in the parameters' autograd metadata and refer back to the
+    wrapper; without ``close()`` wrapper, module and parameters are never collected."""
+    import gc
+    import weakref
+
+    def rank_fn(rank, be):
+        module = _mlp(9)
+        ddp = DistributedDataParallel(module, thread_context(rank, be, dp=1))
+        refs = [weakref.ref(ddp), weakref.ref(module), weakref.ref(module[0].weight)]
+        ddp(torch.randn(2, 6)).sum().backward()
+        ddp.finish_grad_sync()
+        ddp.close()
+        assert not hasattr(module[0].weight, "_nmb_grad_ready")
+        del ddp, module
+        gc.collect()
+        return [r() is None for r in refs]
+
+    (freed,) = run_ranks(1, rank_fn)
+    assert all(freed), freed
