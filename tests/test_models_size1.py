@@ -216,3 +216,6 @@ def test_trainer_on_cpu_follows_the_oracle_trajectory(ctx, name):
     assert mine == pytest.approx(want, rel=1e-6, abs=1e-6)
     assert mine[2] < mine[0]
     trainer.check()
+    assert trainer.graph_settled(True) and trainer.graph_settled(False)      # nothing left to capture on a CPU
+    trainer.close()                                                          # detaches hooks, drops graphs
+    assert not hasattr(next(trainer.model.parameters()), "_nmb_grad_ready")
