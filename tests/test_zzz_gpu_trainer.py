@@ -65,8 +65,9 @@ def test_trainer_step_equals_the_hand_written_loop(ctx, overlap_optimizer):
     assert trainer.graphed, trainer.graph_error
     plan = trainer.ddp._zero_plan
     assert plan is not None and len(plan[1]) > 0           # some parameters are no longer zeroed
-    worst = 0.0
-    for (n, p), q in zip(model.named_parameters(), twin.parameters()):
-        err = (p.float() - q.float()).abs().max().item()
-        worst = max(worst, err / (q.float().abs().max().item() + 1e-6))
-    assert worst < 5e-2, worst
+    # Element-wise bounds are no use here: Adam's update is +-lr whatever the size of the
+    # gradient, and the bf16 atomics of the embedding backward sum in a different order from
+    # run to run, so single elements with a near-zero gradient may move the other way.
+    from tests._numerics import rel_fro
+    worst = max(rel_fro(p, q) for p, q in zip(model.parameters(), twin.parameters()))
+    assert worst < 2e-2, worst
