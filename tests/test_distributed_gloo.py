@@ -309,6 +309,73 @@ def _pp_worker(tp=1, pp=2, microbatches=2, use_ddp=False, sp=False):
     P.destroy_parallel()
 
 
+def _pipeline_trainer_worker(tp=1, pp=2, microbatches=2):
+    """``PipelineTrainer`` (eager 1F1B on a CPU) for two optimisation steps against the
+    oracle's train step on the whole model: loss on the last stage, gradients after
+    ``forward_backward`` and parameters after ``step`` on every stage."""
+    from nano_megatron_b200.engine import PipelineTrainer
+    from nano_megatron_b200.models import build_pipeline_stage_from_reference
+    from nano_megatron_b200.reference import AdamW, shifted_cross_entropy
+    P, ctx = _setup(tensor_parallel_size=tp, pipeline_parallel_size=pp)
+    cfg = _model_cfg(num_layers=4)
+    dp = ctx.data_parallel_size
+    ids = torch.randint(0, cfg.vocab_size, (4 * dp, 16))
+    ref, _, ref_loss = _reference(cfg, ids)
+    stage = build_pipeline_stage_from_reference(ref, ctx)
+    trainer = PipelineTrainer(stage, ctx, num_microbatches=microbatches, lr=1e-2, weight_decay=0.01)
+    assert not trainer.graphed
+    mine = ids[ctx.data_parallel_rank * 4:(ctx.data_parallel_rank + 1) * 4]
+    per = cfg.num_layers // pp
+    offset = ctx.pipeline_parallel_rank * per
+
+    def rename(n):
+        if n.startswith("blocks."):
+            _, idx, rest = n.split(".", 2)
+            return f"blocks.{int(idx) + offset}.{rest}"
+        return n
+
+    def check_loss(loss, want):
+        if P.is_pipeline_last_stage(ctx):
+            avg = loss.detach().clone()
+            if dp > 1:
+                dist.all_reduce(avg, group=ctx.data_parallel_group)
+                avg /= dp
+            _close(avg, want, "pipeline trainer loss")
+        else:
+            assert loss is None
+
+    check_loss(trainer.forward_backward(mine), ref_loss)
+    _check_grads(stage, ref, ctx, cfg, rename)
+    opt = AdamW(ref.named_parameters(), lr=1e-2, weight_decay=0.01)
+    for step in range(2):
+        opt.zero_grad()
+        want = shifted_cross_entropy(ref(ids), ids)
+        want.backward()
+        opt.step()
+        check_loss(trainer.step(mine), want.detach())
+        ref_params = dict(ref.named_parameters())
+        for n, p in stage.named_parameters():
+            # Adam turns a rounding-level difference of a gradient (the data-parallel mean is
+            # summed in another order) into a visible fraction of lr = 1e-2: looser than _close
+            want_p = _expected_shard(rename(n), ref_params[rename(n)].detach(), ctx, cfg)
+            assert torch.allclose(p.detach(), want_p, atol=3e-4, rtol=1e-4), \
+                f"step {step} {n}: max diff {(p.detach() - want_p).abs().max().item()}"
+    trainer.close()
+    P.destroy_parallel()
+
+
+def worker_pipeline_trainer_pp2():
+    _pipeline_trainer_worker()
+
+
+def worker_pipeline_trainer_tp2_pp2():
+    _pipeline_trainer_worker(tp=2)
+
+
+def worker_pipeline_trainer_dp2_pp2():
+    _pipeline_trainer_worker()          # world 4 with pp 2 leaves a data-parallel size of 2
+
+
 def worker_pp2():
     _pp_worker()
 
@@ -402,6 +469,7 @@ CASES = [
     ("worker_groups", 4), ("worker_symmetric_backend_falls_back", 2), ("worker_tp2", 2), ("worker_tp2_fused_gated_gqa", 2), ("worker_tp2_gpt2_tied", 2),
     ("worker_sp2", 2), ("worker_sp2_gpt2", 2), ("worker_sp_equals_tp_on_same_groups", 2),
     ("worker_ddp_mlp", 2), ("worker_ddp_mlp", 4), ("worker_ddp_persistent_mlp", 2), ("worker_tp2_dp2", 4),
+    ("worker_pipeline_trainer_pp2", 2), ("worker_pipeline_trainer_tp2_pp2", 4), ("worker_pipeline_trainer_dp2_pp2", 4),
     ("worker_pp2", 2), ("worker_pp4_m8", 4), ("worker_tp2_pp2", 4), ("worker_tp2_pp2_sp", 4),
     ("worker_dp2_pp2", 4), ("worker_tp2_dp2_pp2", 8), ("worker_cp2", 2), ("worker_cp2_tp2", 4),
     ("worker_cp2_dp2", 4),
