@@ -309,6 +309,56 @@ def _pp_worker(tp=1, pp=2, microbatches=2, use_ddp=False, sp=False):
     P.destroy_parallel()
 
 
+def _trainer_worker(tp=1, sp=False, cp=1):
+    """``Trainer.step`` (zero-grad, forward, loss, backward, gradient sync, AdamW) for two
+    steps on a sharded model against the oracle's train step on the whole model and the
+    whole batch: mean loss over the data / context ranks and every parameter shard."""
+    from nano_megatron_b200.engine import Trainer
+    from nano_megatron_b200.models import build_tp_gpt_from_reference
+    from nano_megatron_b200.reference import AdamW, shifted_cross_entropy
+    P, ctx = _setup(tensor_parallel_size=tp, sequence_parallel=sp, context_parallel_size=cp)
+    cfg = _model_cfg()
+    dp = ctx.data_parallel_size
+    ids = torch.randint(0, cfg.vocab_size, (2 * dp, 16))
+    ref, _, _ = _reference(cfg, ids)
+    model = build_tp_gpt_from_reference(ref, ctx)
+    trainer = Trainer(model, ctx, lr=1e-2, weight_decay=0.01)
+    opt = AdamW(ref.named_parameters(), lr=1e-2, weight_decay=0.01)
+    mine = ids[ctx.data_parallel_rank * 2:(ctx.data_parallel_rank + 1) * 2]
+    for step in range(2):
+        opt.zero_grad()
+        want = shifted_cross_entropy(ref(ids), ids)
+        want.backward()
+        opt.step()
+        mean = trainer.step(mine).detach().clone()
+        dist.all_reduce(mean, group=ctx.data_context_parallel_group)
+        mean /= cp * dp
+        _close(mean, want.detach(), f"step {step} loss")
+        ref_params = dict(ref.named_parameters())
+        for n, p in model.named_parameters():
+            want_p = _expected_shard(n, ref_params[n].detach(), ctx, cfg)
+            assert torch.allclose(p.detach(), want_p, atol=3e-4, rtol=1e-4), \
+                f"step {step} {n}: max diff {(p.detach() - want_p).abs().max().item()}"
+    trainer.close()
+    P.destroy_parallel()
+
+
+def worker_trainer_dp2():
+    _trainer_worker()
+
+
+def worker_trainer_tp2_sp():
+    _trainer_worker(tp=2, sp=True)
+
+
+def worker_trainer_tp2_dp2():
+    _trainer_worker(tp=2)
+
+
+def worker_trainer_cp2():
+    _trainer_worker(cp=2)
+
+
 def _pipeline_trainer_worker(tp=1, pp=2, microbatches=2):
     """``PipelineTrainer`` (eager 1F1B on a CPU) for two optimisation steps against the
     oracle's train step on the whole model: loss on the last stage, gradients after
@@ -469,6 +519,7 @@ CASES = [
     ("worker_groups", 4), ("worker_symmetric_backend_falls_back", 2), ("worker_tp2", 2), ("worker_tp2_fused_gated_gqa", 2), ("worker_tp2_gpt2_tied", 2),
     ("worker_sp2", 2), ("worker_sp2_gpt2", 2), ("worker_sp_equals_tp_on_same_groups", 2),
     ("worker_ddp_mlp", 2), ("worker_ddp_mlp", 4), ("worker_ddp_persistent_mlp", 2), ("worker_tp2_dp2", 4),
+    ("worker_trainer_dp2", 2), ("worker_trainer_tp2_sp", 2), ("worker_trainer_tp2_dp2", 4), ("worker_trainer_cp2", 2),
     ("worker_pipeline_trainer_pp2", 2), ("worker_pipeline_trainer_tp2_pp2", 4), ("worker_pipeline_trainer_dp2_pp2", 4),
     ("worker_pp2", 2), ("worker_pp4_m8", 4), ("worker_tp2_pp2", 4), ("worker_tp2_pp2_sp", 4),
     ("worker_dp2_pp2", 4), ("worker_tp2_dp2_pp2", 8), ("worker_cp2", 2), ("worker_cp2_tp2", 4),
