@@ -16,10 +16,11 @@
 // split-heads / merge-heads / repeat_kv copies of the reference
 // (nano_megatron/model/tp_gpt.py:171-187) exist here.
 //
-// Forward CTA = one 128-row query tile of one head; 192 threads:
-//   warps 0-3  online softmax (one query row per thread), O rescale, epilogue
-//   warp 4     TMA producer (K/V double buffered)
-//   warp 5     TMEM owner + tcgen05.mma issuer
+// Forward CTA = one 128-row query tile of one head; 320 threads:
+//   warps 0-7  online softmax (two threads per query row, 64 columns each), O rescale, epilogue
+//   warp 8     TMA producer (K/V double buffered)
+//   warp 9     TMEM owner + tcgen05.mma issuer
+// Both kernels run on one-dimensional grids ordered longest work first.
 // S = Q K^T lives in TMEM (128 fp32 columns), P is written back to shared
 // memory as a K-major bf16 operand, O accumulates in TMEM.
 //

@@ -227,8 +227,8 @@ class SymmetricWorkspace:
 
     def all_reduce_scale_(self, t: torch.Tensor, scale: float, *, channel: int = CHANNEL_DP, blocks: int = 128) -> None:
         """In-place ``t = sum_over_ranks(t) * scale`` for a tensor from ``alloc_tensor``.
-        ``blocks < 0`` selects the overlap-first kernel (256 threads x 64 registers
-        per block, ``-blocks`` blocks) that fits beside a resident GEMM CTA."""
+        ``blocks < 0`` selects the overlap-first kernel (128 threads x at most 80
+        registers per block, ``-blocks`` blocks) that fits beside a resident GEMM CTA."""
         assert t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous()
         rc = native.lib().nmb_allreduce_scale(
             self.peer_table(t), self.pad.table(), native.ptr(self.epochs), ctypes.c_int(channel),
