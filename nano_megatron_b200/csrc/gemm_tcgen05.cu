@@ -17,11 +17,15 @@
 // Structure: persistent CTAs (one per SM), 320 threads:
 //   warp 0      TMA producer (one elected lane), STAGES-deep smem ring
 //   warp 1      TMEM owner + single-thread tcgen05.mma issuer
-//   warps 2..9  epilogue: tcgen05.ld -> registers -> bias/GELU/residual -> global
+//   warps 2..9  epilogue: tcgen05.ld -> registers -> bias/GELU/residual -> a per-warp
+//               shared-memory transpose -> global in 128-byte row runs
 //               (two warps per TMEM lane quadrant, each takes half of the columns)
 // Two TMEM accumulator buffers let the epilogue of tile i overlap the main
-// loop of tile i+1.  No cluster launch, no multicast: every CTA loads its own
-// tiles.
+// loop of tile i+1.  Every CTA loads its own tiles (no multicast load); the
+// CTA-pair variant further down (cta_group::2, clusters of two) is what the
+// dispatcher picks for shapes with enough tiles.  The kernels are launched with
+// programmatic stream serialization and wait for the previous kernel only
+// after their barrier / TMEM set-up.
 #include "common.cuh"
 
 #include <string.h>
