@@ -18,8 +18,15 @@ B200-first differences:
   nano_megatron/distributed/bucket.py:93); ``finish_grad_sync`` joins the
   streams;
 * when the buffers are in symmetric memory the reduction is one kernel that
-  reads every peer's bucket over NVLink, sums, scales by ``1/(dp*cp)`` and
-  writes the result (``distributed/symm_ops.py``) instead of NCCL + ``div_``;
+  sums, scales by ``1/(dp*cp)`` and writes the result instead of NCCL +
+  ``div_``: in the NVSwitch (``multimem.ld_reduce`` / ``multimem.st``) where the
+  machine offers multicast memory, else by reading every peer's bucket over
+  NVLink (``distributed/symm_mem.py``); the side stream has high priority so
+  that the reduction's few blocks are scheduled beside the compute kernels;
+* with ``overwrite_first_grad`` (what ``Trainer`` asks for) ``zero_grad`` stops
+  zeroing the buffers of parameters whose first gradient write of a step can
+  store instead of add; ``after_bucket_sync`` is a hook a trainer may use to act
+  on a bucket the moment it is reduced; ``close()`` detaches the wrapper;
 * the construction-time broadcast is one coalesced broadcast per dtype, not one
   per parameter (reference :85-96);
 * parameters replicated under sequence parallelism (their TP reduction runs at
