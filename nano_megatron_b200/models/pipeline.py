@@ -42,8 +42,7 @@ class PipelineStage(nn.Module):
     def __init__(self, config: ReferenceGPTConfig, *, pp_rank: int, pp_size: int, tok_emb: Optional[nn.Module],
                  pos_emb: Optional[nn.Module], blocks: nn.ModuleList, ln_f_weight: Optional[Parameter],
                  ln_f_bias: Optional[Parameter], lm_head: Optional[nn.Module], tp_rank: int = 0, tp_size: int = 1,
-                 tp_group: Any = None, tp_backend: Any = None, sequence_parallel: bool = False,
-                 embedder: Optional[TPGPT] = None) -> None:
+                 tp_group: Any = None, tp_backend: Any = None, sequence_parallel: bool = False) -> None:
         super().__init__()
         self.config = config
         self._pp_rank, self._pp_size = pp_rank, pp_size
@@ -60,8 +59,6 @@ class PipelineStage(nn.Module):
         if ln_f_bias is not None:
             self.ln_f_bias = ln_f_bias
         self.lm_head = lm_head
-        # Not registered as a sub-module: only its embed() logic is borrowed.
-        object.__setattr__(self, "_embedder", embedder)
         if self.is_first_stage and self.tok_emb is None:
             raise ValueError("first pipeline stage requires tok_emb")
         if self.is_last_stage and (not hasattr(self, "ln_f_weight") or self.lm_head is None):
