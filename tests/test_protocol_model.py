@@ -21,6 +21,11 @@ owner has not finished reading it for an earlier launch.  The model shows the th
 the comments in the kernel claim: with two alternating buffers the wait never blocks and
 is not even needed, with a single buffer and no wait the race exists, and with a single
 buffer the wait removes it.
+
+The one-launch cross-entropy exchange (``ce_forward_fused_kernel``: every rank stores its
+per-token statistics into all ranks' gather buffer chosen by the parity of a device epoch,
+then the ranks exchange one flag each and read) is the "two buffers, no wait" case of the
+same model.
 """
 from __future__ import annotations
 
